@@ -1,0 +1,2 @@
+// Test infrastructure only: forwards to the standard-library stand-ins.
+#include <boost/_shim.hpp>
