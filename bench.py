@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""Benchmark of the BLSTM training step (frames/s) on 1..8 B200.
+
+    python bench.py --gpus N --steps K --warmup W [--workload cfg1] [--impl reference]
+
+A step is one pass of the hot path over one fraction of synthetic input: load -> forward through
+all layers -> SSE -> BPTT backward -> weight gradients -> [all-reduce] -> steepest-descent update.
+The default workload is configuration 1 (382 -> 2x feedforward_tanh 512 -> 2x blstm 256/direction
+-> 187 -> sse, 32 parallel sequences of 300..1200 frames).  With N > 1 (launched by
+torch.distributed.run, one process per GPU) every rank processes its own fraction of that shape
+and the weight gradients are summed with NCCL before the update (weak scaling).
+
+`value`  : real (unpadded) frames of all ranks per second, inputs already resident in HBM,
+           timed with CUDA events on the library's stream, max over ranks.
+`e2e`    : the same metric through b2_net_train_step with pinned HOST buffers: the host->device
+           copy of the fraction and the device->host read of the error are inside the timed region.
+`--impl reference` times the reference toolkit's own Cpu-device code (oracle/_ref, OpenMP Thrust
+host backend, all host threads; the C restatement if that library did not travel) on a bounded
+sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "project-currennt-public_b200"))
+
+METRIC = "blstm_train_step_frames_per_sec"
+UNIT = "frames/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=float(d["hbm_gbs"]), bf16=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), src="measured")
+    return dict(hbm=6650.0, bf16=1400.0, src="fallback")
+
+
+class ClockSampler(threading.Thread):
+    """samples nvidia-smi clocks and throttle reasons while the timed region runs"""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.rows = index, False, []
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.2)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower() == "active" for r in self.rows if len(r) > 2 + i)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None,
+                "sm_max_mhz": int(self.rows[0][1]) if self.rows[0][1].isdigit() else None, "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def workload_for(name, rank):
+    from b2lstm import workloads
+    cfg = int(name.replace("cfg", ""))
+    return cfg, workloads.build(cfg, rank=rank)
+
+
+# ---- algorithmic work per phase (per step, this rank) -----------------------------------------------
+def phase_work(layers, T, P, real_frames):
+    """{phase: (kind, amount)}: flops for GEMM phases (padded frames: the kernels process them),
+    bytes for HBM phases (40 B forward / 44 B backward per cell-step of a real or padded frame)."""
+    N = T * P
+    w = {}
+
+    def add(k, kind, v):
+        w[k] = (kind, w.get(k, (kind, 0))[1] + v)
+    for i in range(1, len(layers)):
+        ty, ls, pls = layers[i]["type"], layers[i]["size"], layers[i - 1]["size"]
+        if ty.startswith("feedforward"):
+            add("ff_forward_gemm", "flops", 2.0 * ls * pls * N)
+            add("ff_backward_gemm", "flops", 2.0 * ls * pls * N * (2 if i > 1 else 1))
+            add("ff_bias_act", "bytes", 8.0 * ls * N)
+            add("ff_delta", "bytes", 12.0 * ls * N)
+            add("ff_bias_grad", "bytes", 4.0 * ls * N)
+        elif ty in ("lstm", "blstm"):
+            els = ls // 2 if ty == "blstm" else ls
+            add("lstm_proj_gemm", "flops", 8.0 * ls * pls * N)
+            add("lstm_dx_gemm", "flops", 8.0 * ls * pls * N if i > 1 else 0.0)
+            add("lstm_dw_in_gemm", "flops", 8.0 * ls * pls * N)
+            add("lstm_dw_rec_gemm", "flops", 8.0 * ls * els * (N - P))
+            add("lstm_fwd_recurrence", "bytes", 40.0 * ls * N)
+            add("lstm_bwd_recurrence", "bytes", 44.0 * ls * N)
+            add("lstm_fwd_recurrence_flops", "flops", 8.0 * ls * els * (N - P))
+            add("lstm_bwd_recurrence_flops", "flops", 8.0 * ls * els * (N - P))
+            add("lstm_vector_grads", "bytes", 28.0 * ls * N)
+        elif ty == "sse":
+            add("sse_loss", "bytes", 8.0 * ls * N)
+            add("sse_grad", "bytes", 12.0 * ls * N)
+    return w
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the reference's own Cpu code on the host cores, bounded sample of the workload."""
+    if rank != 0:
+        return
+    os.environ.setdefault("OMP_NUM_THREADS", str(os.cpu_count() or 1))
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from oracle import OracleNet, ref_available
+    from b2lstm import workloads
+    cfg = int(args.workload.replace("cfg", ""))
+    kind = "ref_omp" if ref_available(omp=True) else "port"
+    cores = (os.cpu_count() or 1) if kind == "ref_omp" else 1
+    # bounded sample: the configuration's layer sizes on P_s sequences of reduced length
+    c = workloads.CONFIGS[cfg]
+    P_s = min(c["P"], 8)
+    scale = args.cpu_scale
+
+    def one(scale):
+        wl = workloads.build(cfg, scale_frames=scale, P=P_s)
+        net = OracleNet(wl["layers"], P_s, int(wl["lens"].max()), kind)
+        for i, w in wl["weights"].items():
+            net.set_weights(i, w)
+        t0 = time.perf_counter()
+        net.load(wl["lens"], wl["x"], wl["tg"])
+        net.forward()
+        net.backward()
+        net.sgd_update(1e-5, 0.9)
+        dt = time.perf_counter() - t0
+        net.close()
+        return int(wl["lens"].sum()), dt
+    frames, dt = one(scale)          # calibration doubles as warm-up
+    target = args.cpu_seconds / max(1, args.steps + args.warmup)
+    scale2 = min(1.0, max(scale, scale * target / max(dt, 1e-3)))
+    for _ in range(max(0, args.warmup - 1)):
+        one(scale2)
+    tot_f, tot_t = 0, 0.0
+    for _ in range(args.steps):
+        f, t = one(scale2)
+        tot_f += f
+        tot_t += t
+    v = tot_f / tot_t
+    sample = "%s layer sizes, %d sequences x ~%d frames per step (%d real frames/step), %d steps" % (
+        args.workload, P_s, int(c["len_hi"] * scale2), tot_f // max(1, args.steps), args.steps)
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * tot_t / max(1, args.steps), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workloads.CONFIGS[cfg]["name"], "sample": sample},
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "reference" if kind == "ref_omp" else "port",
+                             "sample": sample},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b2lstm", choices=["b2lstm", "reference"])
+    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--strong", action="store_true", help="split the workload's sequences over the ranks (cfg4)")
+    ap.add_argument("--recurrence", type=int, default=1)
+    ap.add_argument("--ffma", type=int, default=0)
+    ap.add_argument("--cpu-seconds", type=float, default=20.0, help="budget of the CPU baseline sample")
+    ap.add_argument("--cpu-scale", type=float, default=0.02)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b2lstm" else max(args.warmup, 1)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import b2lstm
+    from b2lstm import workloads
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    cfg = int(args.workload.replace("cfg", ""))
+    c = workloads.CONFIGS[cfg]
+    if args.strong and world > 1:
+        full = workloads.build(cfg)
+        idx = np.arange(rank, c["P"], world)       # deal the length-sorted sequences round-robin
+        wl = dict(full, P=len(idx), lens=full["lens"][idx], x=np.ascontiguousarray(full["x"][:, idx]),
+                  tg=np.ascontiguousarray(full["tg"][:, idx]))
+        T = int(wl["lens"].max())
+        wl["x"], wl["tg"] = wl["x"][:T], wl["tg"][:T]
+    else:
+        wl = workloads.build(cfg, rank=rank)
+    layers, P, lens = wl["layers"], wl["P"], wl["lens"]
+    T = int(lens.max())
+    real_frames = int(lens.sum())
+
+    net = b2lstm.Net(layers, P, T)
+    net.set_recurrence_mode(args.recurrence)
+    net.set_force_ffma(args.ffma)
+    for i, w in wl["weights"].items():
+        net.set_weights(i, w)
+    if world > 1:
+        idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            idt.copy_(torch.frombuffer(bytearray(b2lstm.dp_unique_id()), dtype=torch.uint8))
+        dist.broadcast(idt, 0)
+        net.dp_attach(rank, world, bytes(idt.cpu().numpy().tobytes()))
+
+    x_host = torch.from_numpy(wl["x"]).pin_memory()
+    t_host = torch.from_numpy(wl["tg"]).pin_memory()
+    x_dev, t_dev = x_host.cuda(), t_host.cuda()
+    lr, mom = 1e-6, 0.9
+    ext = torch.cuda.ExternalStream(net.stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(ext)
+        for _ in range(steps):
+            fn()
+        e1.record(ext)
+        net.synchronize()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    step_dev = lambda: net.train_step_dev(lens, T, x_dev, t_dev, lr, mom)
+    step_e2e = lambda: net.train_step(lens, x_host.numpy(), t_host.numpy(), lr, mom, want_error=True)
+
+    for _ in range(args.warmup):
+        step_dev()
+    net.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    l0 = net.launch_count
+    net.set_profiling(True)
+    ms = timed(step_dev, args.steps)
+    prof = net.get_profile()
+    net.set_profiling(False)
+    launches = net.launch_count - l0
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    sampler.stop_flag = True
+    sampler.join(timeout=3)
+
+    frames_all = real_frames
+    if world > 1:
+        t = torch.tensor([real_frames], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t)
+        frames_all = int(t.item())
+    value = frames_all * args.steps / (ms * 1e-3)
+    e2e = frames_all * args.steps / (ms_e2e * 1e-3)
+
+    if rank == 0:
+        pk = peaks()
+        work = phase_work(layers, T, P, real_frames)
+        kernels = {}
+        for name, (tms, ln) in prof.items():
+            per = tms / args.steps
+            ent = {"ms_per_step": round(per, 4), "launches_per_step": ln // args.steps, "share": round(tms / ms, 4)}
+            if name in work and per > 0:
+                kind, amt = work[name]
+                if kind == "flops":
+                    ent["tflops"] = round(amt / (per * 1e-3) / 1e12, 3)
+                else:
+                    ent["gbs"] = round(amt / (per * 1e-3) / 1e9, 2)
+                    fl = work.get(name + "_flops")
+                    if fl:
+                        ent["tflops"] = round(fl[1] / (per * 1e-3) / 1e12, 3)
+            kernels[name] = ent
+        top = max((k for k in kernels if k in work), key=lambda k: kernels[k]["ms_per_step"])
+        kind, amt = work[top]
+        per_launch = kernels[top]["ms_per_step"] * 1e-3
+        if kind == "flops":
+            peak = pk["bf16"] / 6.0   # 3xTF32: TF32 dense = bf16/2, three MMAs per fp32 product
+            roof = {"bound": "tensor", "kernel": top, "achieved": amt / per_launch / 1e12, "peak": peak, "unit": "TFLOP/s",
+                    "peak_note": "%s bf16 dense sustained / 6 (3xTF32 fp32 emulation)" % pk["src"]}
+        else:
+            roof = {"bound": "hbm", "kernel": top, "achieved": amt / per_launch / 1e9, "peak": pk["hbm"], "unit": "GB/s",
+                    "peak_note": "%s copy bandwidth" % pk["src"]}
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        roof["traffic"] = None
+        roof["share_of_step"] = kernels[top]["share"]
+        in_b = int(x_host.numel() * 4 + t_host.numel() * 4 + T * P)
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if args.strong else "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": c["name"], "parallel_sequences_per_gpu": P, "max_frames": T,
+                           "real_frames_per_gpu_step": real_frames, "parallelism": "dp%d" % world,
+                           "recurrence": "persistent" if args.recurrence else "stepwise",
+                           "gemm": "ffma" if args.ffma else "tcgen05_3xtf32",
+                           "l2": "working set per step (GBs of state buffers) exceeds the 126 MB L2; no flush needed"},
+                "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": in_b,
+                        "d2h_bytes_per_step": 8},
+                "gpu_launches": launches, "roofline": roof, "kernels": kernels, "clocks": sampler.summary()}
+        if world == 1 and not args.no_cpu_baseline:
+            try:
+                out = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--workload", args.workload,
+                                      "--steps", "2", "--warmup", "1", "--cpu-seconds", str(args.cpu_seconds)],
+                                     capture_output=True, text=True, timeout=600)
+                ref_line = [l for l in out.stdout.splitlines() if l.startswith("{")][-1]
+                line["cpu_baseline"] = json.loads(ref_line)["cpu_baseline"]
+            except Exception as ex:  # the baseline is a reported extra; never lose the GPU line over it
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": "failed: %r" % (ex,)}
+        print(json.dumps(line), flush=True)
+    net.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

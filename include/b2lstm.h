@@ -1,0 +1,195 @@
+/*
+ * b2lstm -- B200 (sm_100a) implementation of the CURRENNT peephole LSTM / BLSTM training path.
+ *
+ * C ABI.  Plain pointers and sizes only; every function returns an int status (0 = ok, negative
+ * = error, text via b2_last_error_string()).  Nothing here throws, traps or falls back to the
+ * CPU: when the CUDA device or a kernel is unavailable the call fails with B2_ERR_CUDA.
+ *
+ * Conventions kept from the reference toolkit (paths are inside CURRENNT_codes/currennt_lib/src/):
+ *   - activations are time-major with the parallel sequences interleaved: element d of frame
+ *     (t, p) sits at [(t*P + p)*dim + d]                         (data_sets/DataSet.cpp:853-861)
+ *   - matrices are column-major views over such vectors          (helpers/Matrix.cu:202-211)
+ *   - pattern types: char per frame, 0 NONE (padding), 1 FIRST, 2 NORMAL, 3 LAST (Types.hpp:35-38)
+ *   - the (b)lstm weight vector is [input | bias | recurrent | peephole]
+ *                                                                (layers/LstmLayer.hpp:36-55)
+ *   - a blstm's "size" is the total over both directions         (layers/LstmLayer.cu:1091-1098)
+ *   - gradients are sums over frames, never averaged             (optimizers/SteepestDescentOptimizer.cu:421-438)
+ *
+ * Three levels, lowest first:
+ *   b2_matrix_*   the GEMM wrapper                      <-> helpers::Matrix / helpers::cublas
+ *   b2_lstm_*     one (b)lstm layer on caller's buffers <-> layers::LstmLayer<Gpu>
+ *   b2_net_*      layer stack + minibatch step          <-> NeuralNetwork + Optimizer::_processDataSet
+ *   b2_dp_*       gradient all-reduce across GPUs (no counterpart: the reference is single-GPU)
+ */
+#ifndef B2LSTM_H
+#define B2LSTM_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t without pulling the CUDA headers into the caller */
+typedef void *b2_stream;
+
+enum {
+    B2_OK = 0,
+    B2_ERR_BAD_SHAPE = -1,    /* sizes inconsistent with the descriptor / allocation        */
+    B2_ERR_CUDA = -2,         /* a CUDA runtime call or kernel launch failed                 */
+    B2_ERR_STEP_TIMEOUT = -3, /* a bounded device-side wait in a persistent kernel ran out   */
+    B2_ERR_NCCL = -4,         /* NCCL missing or a collective failed                         */
+    B2_ERR_BAD_ARG = -5,      /* null pointer, unknown layer type, malformed JSON ...        */
+    B2_ERR_STATE = -6         /* call order violated (e.g. backward before forward)          */
+};
+
+const char *b2_last_error_string(void);
+/* Library build id, e.g. "b2lstm 0.1 sm_100a". */
+const char *b2_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * helpers::Matrix<Gpu>::assignProduct / addProduct          (helpers/Matrix.cu:354-377,
+ * helpers/cublas.cu:52-84: cublasSgemm with alpha = 1, beta = 0 or 1).
+ * C(m x n) = op(A) op(B) (+ C if accumulate), all column-major device pointers with leading
+ * dimensions lda/ldb/ldc; op = transpose when the flag is non-zero.  The reference rejects
+ * (transA && transB) (Matrix.cu:259-260); so does this call (B2_ERR_BAD_ARG).
+ * Runs on tensor cores (3xTF32, fp32 accumulate) when the shape qualifies, otherwise as an
+ * FFMA kernel; `force_ffma` non-zero always selects the latter.
+ * ------------------------------------------------------------------------------------------ */
+int b2_matrix_multiply(float *C, int ldc, const float *A, int lda, int transA, const float *B, int ldb,
+                       int transB, int m, int n, int k, int accumulate, int force_ffma, b2_stream stream);
+
+/* ------------------------------------------------------------------------------------------
+ * layers::LstmLayer<Gpu>                                    (layers/LstmLayer.hpp:168-308)
+ * ------------------------------------------------------------------------------------------ */
+typedef struct b2_lstm b2_lstm;
+
+typedef struct {
+    int parallel_sequences; /* P, Layer::parallelSequences()                                   */
+    int max_seq_length;     /* frames per sequence the buffers are sized for (Layer::maxSeqLength) */
+    int prev_size;          /* size of the preceding layer                                     */
+    int size;               /* layer size; TOTAL over both directions for a blstm              */
+    int bidirectional;      /* 0 "lstm", 1 "blstm"                   (LayerFactory.cu:127-132) */
+    float bias;             /* the layer's JSON "bias" value         (TrainableLayer.cu:108-109) */
+} b2_lstm_desc;
+
+/* ls*(4*(pls+1) + 4*els + 3)                                 (layers/LstmLayer.cu:1085-1088) */
+size_t b2_lstm_num_weights(const b2_lstm_desc *desc);
+/* LstmLayer constructor (LstmLayer.cu:1079-1376): allocates the private state buffers on the
+ * current CUDA device.  The layer keeps NO weights, outputs or errors of its own: those stay in
+ * the caller's vectors and are passed to every call. */
+int b2_lstm_create(const b2_lstm_desc *desc, b2_lstm **out);
+void b2_lstm_destroy(b2_lstm *layer);
+/* LstmLayer::loadSequences (LstmLayer.cu:1489-1533, Layer.cu:254-305): take over the current
+ * fraction's shape.  pat_types_dev: device char[cur_max_len * P]. */
+int b2_lstm_load_sequences(b2_lstm *layer, int cur_max_len, int cur_min_len, const char *pat_types_dev);
+/* LstmLayer::computeForwardPass (LstmLayer.cu:1744-1949).
+ * weights_dev: b2_lstm_num_weights floats; x_dev: prev_size x (T*P) = precedingLayer().outputs();
+ * y_dev: size x (T*P) = outputs(), forward-direction units first, then backward-direction units.
+ * Padding frames of y are written as exact zeros. */
+int b2_lstm_forward(b2_lstm *layer, const float *weights_dev, const float *x_dev, float *y_dev, b2_stream stream);
+/* LstmLayer::computeBackwardPass (LstmLayer.cu:2067-2382).
+ * dy_dev: size x (T*P) = outputErrors() (read only); dx_dev: prev_size x (T*P) =
+ * precedingLayer().outputErrors(), OVERWRITTEN (may be NULL to skip it, as for an input layer
+ * nobody reads); dw_dev: weightUpdates(), OVERWRITTEN, same layout as the weights. */
+int b2_lstm_backward(b2_lstm *layer, const float *weights_dev, const float *x_dev, const float *y_dev,
+                     const float *dy_dev, float *dx_dev, float *dw_dev, b2_stream stream);
+/* Which recurrence kernels run: 0 = one launch per timestep, 1 = persistent kernel (default). */
+int b2_lstm_set_recurrence_mode(b2_lstm *layer, int mode);
+/* Bytes of private device memory the layer holds. */
+size_t b2_lstm_state_bytes(const b2_lstm *layer);
+
+/* ------------------------------------------------------------------------------------------
+ * NeuralNetwork + Optimizer::_processDataSet + SteepestDescentOptimizer
+ * (NeuralNetwork.cpp:1056-1086,1367-1373,1734-1742,2864-2873,2982-2989;
+ *  optimizers/Optimizer.cu:45-258; optimizers/SteepestDescentOptimizer.cu:74-100,421-438)
+ * ------------------------------------------------------------------------------------------ */
+typedef struct b2_net b2_net;
+
+/* network_json: the reference's network file ({"layers":[{"size","name","type","bias",
+ * "learningRate"?}, ...], "weights"?: {name: {"input":[..],"bias":[..],"internal":[..]}}}),
+ * NeuralNetwork.cpp:1056-1086, TrainableLayer.cu:135-205.  Layer types understood: input,
+ * feedforward_tanh, feedforward_logistic, feedforward_identity, lstm, blstm, sse.
+ * Weights absent from the JSON are drawn U(-0.08, 0.08)... by seed `random_seed`. */
+int b2_net_create(const char *network_json, int parallel_sequences, int max_seq_length, unsigned random_seed,
+                  b2_net **out);
+void b2_net_destroy(b2_net *net);
+int b2_net_num_layers(const b2_net *net);
+int b2_net_layer_size(const b2_net *net, int layer);
+/* 0 for layers without weights */
+size_t b2_net_num_weights(const b2_net *net, int layer);
+/* host <-> device copies of one layer's weight vector / weightUpdates vector */
+int b2_net_set_weights(b2_net *net, int layer, const float *host_w);
+int b2_net_get_weights(b2_net *net, int layer, float *host_w);
+int b2_net_get_weight_updates(b2_net *net, int layer, float *host_g);
+/* device addresses of a layer's vectors, for callers that stay on the GPU */
+float *b2_net_weights_dev(b2_net *net, int layer);
+float *b2_net_weight_updates_dev(b2_net *net, int layer);
+float *b2_net_outputs_dev(b2_net *net, int layer);
+float *b2_net_output_errors_dev(b2_net *net, int layer);
+
+/* NeuralNetwork::loadSequences(fraction) (NeuralNetwork.cpp:1367-1373): host buffers in the
+ * fraction layout of DataSet::_makeFractionTask (DataSet.cpp:642-1022): inputs[T*P*in],
+ * targets[T*P*out], padded frames zero; seq_lens[n_seqs], n_seqs <= P; T >= max(seq_lens).
+ * Pattern types are derived from the lengths.  Copies host -> device (asynchronously when the
+ * host buffers are pinned). */
+int b2_net_load_fraction(b2_net *net, int T, int n_seqs, const int *seq_lens, const float *host_inputs,
+                         const float *host_targets);
+/* The same with inputs/targets already on the device (they are copied device -> device). */
+int b2_net_load_fraction_dev(b2_net *net, int T, int n_seqs, const int *seq_lens, const float *dev_inputs,
+                             const float *dev_targets);
+/* NeuralNetwork::computeForwardPass then calculateError: *error = 0.5*sum (target-output)^2 over
+ * non-padding frames (SsePostOutputLayer.cu:94-116,197-209).  Synchronises to return the scalar;
+ * pass NULL to stay asynchronous. */
+int b2_net_forward(b2_net *net, double *error);
+/* NeuralNetwork::computeBackwardPass (layers in reverse order, NeuralNetwork.cpp:2744-2800). */
+int b2_net_backward(b2_net *net);
+/* SteepestDescentOptimizer::_updateWeights, plain branch: g<-0 where NaN/Inf;
+ * delta<-momentum*delta-lr*g; w<-w+delta.  A layer's own "learningRate" (>= 0) overrides lr
+ * (SteepestDescentOptimizer.cu:425-426).  With a data-parallel communicator attached the
+ * gradients are first summed over all ranks. */
+int b2_net_update_weights(b2_net *net, float learning_rate, float momentum);
+/* One iteration of the minibatch loop of Optimizer::_processDataSet (Optimizer.cu:68-231) with
+ * hybrid_online_batch: load, forward, error, backward, [all-reduce], update.  *error may be NULL. */
+int b2_net_train_step(b2_net *net, int T, int n_seqs, const int *seq_lens, const float *host_inputs,
+                      const float *host_targets, float learning_rate, float momentum, double *error);
+/* Device-resident variant of the step above (no host<->device traffic, no synchronisation). */
+int b2_net_train_step_dev(b2_net *net, int T, int n_seqs, const int *seq_lens, const float *dev_inputs,
+                          const float *dev_targets, float learning_rate, float momentum);
+/* Copy a layer's outputs / output errors of the current fraction to the host: T*P*size floats. */
+int b2_net_get_outputs(b2_net *net, int layer, float *host_out);
+int b2_net_get_output_errors(b2_net *net, int layer, float *host_out);
+/* Waits for everything the net has enqueued; returns B2_ERR_STEP_TIMEOUT / B2_ERR_CUDA if a
+ * kernel reported a problem since the last call. */
+int b2_net_synchronize(b2_net *net);
+/* The stream all of the net's work is ordered on (a cudaStream_t). */
+b2_stream b2_net_stream(b2_net *net);
+/* 0 = stepwise recurrence kernels, 1 = persistent (default); applies to every (b)lstm layer. */
+int b2_net_set_recurrence_mode(b2_net *net, int mode);
+/* Non-zero forces the FFMA GEMM everywhere (the tensor-core GEMM is the default). */
+int b2_net_set_force_ffma(b2_net *net, int on);
+/* Number of kernels this library has launched on behalf of `net` since creation. */
+unsigned long long b2_net_launch_count(const b2_net *net);
+/* Per-kernel-class device time of the LAST train step, measured with CUDA events when
+ * profiling is switched on (costs extra synchronisation).  names/ms arrays of length `cap`;
+ * returns the number of entries. */
+int b2_net_set_profiling(b2_net *net, int on);
+int b2_net_get_profile(b2_net *net, int cap, const char **names, float *ms, int *launches);
+
+/* ------------------------------------------------------------------------------------------
+ * Data-parallel training: sequences of a fraction are dealt to the ranks, every rank holds a
+ * full weight replica, weightUpdates are summed with ncclAllReduce before the update.
+ * No counterpart in the reference (single GPU, single process).
+ * ------------------------------------------------------------------------------------------ */
+#define B2_DP_UNIQUE_ID_BYTES 128
+/* rank 0 creates the id and ships the 128 bytes to the other ranks by any means */
+int b2_dp_get_unique_id(void *id_bytes);
+int b2_dp_attach(b2_net *net, int rank, int world_size, const void *id_bytes);
+int b2_dp_detach(b2_net *net);
+/* Sum a double over all ranks (loss / frame counts). Synchronises. */
+int b2_dp_allreduce_scalar(b2_net *net, double *value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2LSTM_H */

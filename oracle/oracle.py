@@ -53,6 +53,24 @@ def _load(kind):
     return lib, pre
 
 
+class _quiet_stdout:
+    """The reference's constructors print progress lines with printf; keep them out of the
+    caller's stdout (a benchmark prints exactly one JSON line there)."""
+
+    def __enter__(self):
+        import sys
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        null = os.open(os.devnull, os.O_WRONLY)
+        os.dup2(null, 1)
+        os.close(null)
+
+    def __exit__(self, *a):
+        C.CDLL(None).fflush(None)
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+
+
 class OracleNet:
     """layers: list of dicts with keys type, size and (trainable layers) bias, as in network.jsn."""
 
@@ -61,7 +79,8 @@ class OracleNet:
         self.lib, self.pre = _load(kind)
         if kind.startswith("ref"):
             js = json.dumps({"layers": [dict({"name": "l%d" % i, "bias": 1.0}, **l) for i, l in enumerate(layers)]})
-            self.h = C.c_void_p(self._f("create")(js.encode(), P, maxT))
+            with _quiet_stdout():
+                self.h = C.c_void_p(self._f("create")(js.encode(), P, maxT))
             if not self.h:
                 self.lib.ref_last_error.restype = C.c_char_p
                 raise RuntimeError(self.lib.ref_last_error().decode())

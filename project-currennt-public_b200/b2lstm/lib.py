@@ -1,0 +1,303 @@
+"""ctypes bindings of include/b2lstm.h.
+
+Net mirrors the call order of the reference toolkit's training loop (Optimizer::_processDataSet,
+optimizers/Optimizer.cu:68-231 of the reference): load_fraction -> forward (returns the SSE) ->
+backward -> update_weights, or train_step for all of it.  LstmLayer mirrors layers::LstmLayer on
+caller-owned device buffers (any object with a data_ptr(), e.g. torch CUDA tensors).
+"""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def library_path():
+    return os.path.join(os.path.dirname(_HERE), "libb2lstm.so")
+
+
+class B2Error(RuntimeError):
+    pass
+
+
+_fp = C.POINTER(C.c_float)
+_ip = C.POINTER(C.c_int)
+
+# name -> (restype, argtypes); mirrors include/b2lstm.h one to one
+SIGNATURES = {
+    "b2_last_error_string": (C.c_char_p, []),
+    "b2_version": (C.c_char_p, []),
+    "b2_matrix_multiply": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int,
+                                     C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "b2_lstm_num_weights": (C.c_size_t, [C.c_void_p]),
+    "b2_lstm_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "b2_lstm_destroy": (None, [C.c_void_p]),
+    "b2_lstm_load_sequences": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "b2_lstm_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b2_lstm_backward": (C.c_int, [C.c_void_p] * 8),
+    "b2_lstm_set_recurrence_mode": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2_lstm_state_bytes": (C.c_size_t, [C.c_void_p]),
+    "b2_net_create": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_uint, C.POINTER(C.c_void_p)]),
+    "b2_net_destroy": (None, [C.c_void_p]),
+    "b2_net_num_layers": (C.c_int, [C.c_void_p]),
+    "b2_net_layer_size": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2_net_num_weights": (C.c_size_t, [C.c_void_p, C.c_int]),
+    "b2_net_set_weights": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "b2_net_get_weights": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "b2_net_get_weight_updates": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "b2_net_weights_dev": (C.c_void_p, [C.c_void_p, C.c_int]),
+    "b2_net_weight_updates_dev": (C.c_void_p, [C.c_void_p, C.c_int]),
+    "b2_net_outputs_dev": (C.c_void_p, [C.c_void_p, C.c_int]),
+    "b2_net_output_errors_dev": (C.c_void_p, [C.c_void_p, C.c_int]),
+    "b2_net_load_fraction": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b2_net_load_fraction_dev": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b2_net_forward": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
+    "b2_net_backward": (C.c_int, [C.c_void_p]),
+    "b2_net_update_weights": (C.c_int, [C.c_void_p, C.c_float, C.c_float]),
+    "b2_net_train_step": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float,
+                                    C.c_float, C.POINTER(C.c_double)]),
+    "b2_net_train_step_dev": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float,
+                                        C.c_float]),
+    "b2_net_get_outputs": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "b2_net_get_output_errors": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "b2_net_synchronize": (C.c_int, [C.c_void_p]),
+    "b2_net_stream": (C.c_void_p, [C.c_void_p]),
+    "b2_net_set_recurrence_mode": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2_net_set_force_ffma": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2_net_launch_count": (C.c_ulonglong, [C.c_void_p]),
+    "b2_net_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2_net_get_profile": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_char_p), _fp, _ip]),
+    "b2_dp_get_unique_id": (C.c_int, [C.c_void_p]),
+    "b2_dp_attach": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "b2_dp_detach": (C.c_int, [C.c_void_p]),
+    "b2_dp_allreduce_scalar": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded shared library.  Raises if it has not been built: there is no other code path."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise B2Error("%s is missing: build it with `make -C %s/csrc` (or __graft_entry__.build())"
+                          % (path, os.path.dirname(_HERE)))
+        _lib = C.CDLL(path, mode=C.RTLD_GLOBAL)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(_lib, name)
+            fn.restype = res
+            fn.argtypes = args
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise B2Error("b2lstm error %d: %s" % (rc, lib().b2_last_error_string().decode()))
+
+
+def _dev(x):
+    """device address of a tensor-like object (or a raw int / None)"""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    return x.data_ptr()
+
+
+class _LstmDesc(C.Structure):
+    _fields_ = [("parallel_sequences", C.c_int), ("max_seq_length", C.c_int), ("prev_size", C.c_int),
+                ("size", C.c_int), ("bidirectional", C.c_int), ("bias", C.c_float)]
+
+
+def lstm_num_weights(prev_size, size, bidirectional):
+    d = _LstmDesc(1, 1, prev_size, size, int(bidirectional), 1.0)
+    return int(lib().b2_lstm_num_weights(C.byref(d)))
+
+
+def matrix_multiply(Cm, ldc, A, lda, transA, B, ldb, transB, m, n, k, accumulate=False, force_ffma=False, stream=None):
+    _check(lib().b2_matrix_multiply(_dev(Cm), ldc, _dev(A), lda, int(transA), _dev(B), ldb, int(transB), m, n, k,
+                                    int(accumulate), int(force_ffma), stream))
+
+
+class LstmLayer:
+    """layers::LstmLayer on caller-owned device buffers (see include/b2lstm.h)."""
+
+    def __init__(self, parallel_sequences, max_seq_length, prev_size, size, bidirectional, bias=1.0):
+        self.desc = _LstmDesc(parallel_sequences, max_seq_length, prev_size, size, int(bidirectional), bias)
+        self.h = C.c_void_p()
+        _check(lib().b2_lstm_create(C.byref(self.desc), C.byref(self.h)))
+        self.num_weights = int(lib().b2_lstm_num_weights(C.byref(self.desc)))
+
+    def close(self):
+        if self.h:
+            lib().b2_lstm_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def load_sequences(self, cur_max_len, cur_min_len, pat_types_dev):
+        _check(lib().b2_lstm_load_sequences(self.h, cur_max_len, cur_min_len, _dev(pat_types_dev)))
+
+    def forward(self, weights, x, y, stream=None):
+        _check(lib().b2_lstm_forward(self.h, _dev(weights), _dev(x), _dev(y), stream))
+
+    def backward(self, weights, x, y, dy, dx, dw, stream=None):
+        _check(lib().b2_lstm_backward(self.h, _dev(weights), _dev(x), _dev(y), _dev(dy), _dev(dx), _dev(dw), stream))
+
+    def set_recurrence_mode(self, mode):
+        _check(lib().b2_lstm_set_recurrence_mode(self.h, mode))
+
+    @property
+    def state_bytes(self):
+        return int(lib().b2_lstm_state_bytes(self.h))
+
+
+def dp_unique_id():
+    buf = C.create_string_buffer(128)
+    _check(lib().b2_dp_get_unique_id(buf))
+    return buf.raw
+
+
+class Net:
+    """NeuralNetwork + steepest-descent step.  layers: list of dicts as in the reference's network.jsn."""
+
+    def __init__(self, layers, parallel_sequences, max_seq_length, seed=1234, weights=None):
+        doc = {"layers": [dict({"name": "l%d" % i}, **l) for i, l in enumerate(layers)]}
+        if weights is not None:
+            doc["weights"] = weights
+        self.layers = doc["layers"]
+        self.P, self.maxT = parallel_sequences, max_seq_length
+        self.h = C.c_void_p()
+        _check(lib().b2_net_create(json.dumps(doc).encode(), parallel_sequences, max_seq_length, seed, C.byref(self.h)))
+        self.T = 0
+
+    def close(self):
+        if self.h:
+            lib().b2_net_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def num_weights(self, i):
+        return int(lib().b2_net_num_weights(self.h, i))
+
+    def set_weights(self, i, w):
+        w = np.ascontiguousarray(w, np.float32)
+        if w.size != self.num_weights(i):
+            raise B2Error("layer %d takes %d weights, got %d" % (i, self.num_weights(i), w.size))
+        _check(lib().b2_net_set_weights(self.h, i, w.ctypes.data))
+
+    def get_weights(self, i):
+        w = np.empty(self.num_weights(i), np.float32)
+        _check(lib().b2_net_get_weights(self.h, i, w.ctypes.data))
+        return w
+
+    def weight_updates(self, i):
+        g = np.empty(self.num_weights(i), np.float32)
+        _check(lib().b2_net_get_weight_updates(self.h, i, g.ctypes.data))
+        return g
+
+    def _lens(self, lens):
+        lens = np.ascontiguousarray(lens, np.int32)
+        self.T = int(lens.max())
+        return lens
+
+    def load_fraction(self, lens, inputs, targets):
+        """Host arrays: inputs [T,P,in], targets [T,P,out] float32 (padding zero); lens of the real sequences."""
+        lens = self._lens(lens)
+        inputs = np.ascontiguousarray(inputs, np.float32)
+        targets = np.ascontiguousarray(targets, np.float32)
+        _check(lib().b2_net_load_fraction(self.h, inputs.shape[0], len(lens), lens.ctypes.data, inputs.ctypes.data,
+                                          targets.ctypes.data))
+        _check(lib().b2_net_synchronize(self.h))   # the host arrays may go away after this call
+
+    def load_fraction_dev(self, lens, T, inputs_dev, targets_dev):
+        lens = self._lens(lens)
+        _check(lib().b2_net_load_fraction_dev(self.h, T, len(lens), lens.ctypes.data, _dev(inputs_dev), _dev(targets_dev)))
+
+    def forward(self):
+        e = C.c_double()
+        _check(lib().b2_net_forward(self.h, C.byref(e)))
+        return e.value
+
+    def backward(self):
+        _check(lib().b2_net_backward(self.h))
+
+    def update_weights(self, lr, momentum):
+        _check(lib().b2_net_update_weights(self.h, lr, momentum))
+
+    def train_step(self, lens, inputs, targets, lr, momentum, want_error=True):
+        """inputs/targets: host arrays (numpy, or pinned torch CPU tensors via .numpy())."""
+        lens = self._lens(lens)
+        e = C.c_double()
+        _check(lib().b2_net_train_step(self.h, inputs.shape[0], len(lens), lens.ctypes.data, inputs.ctypes.data,
+                                       targets.ctypes.data, lr, momentum, C.byref(e) if want_error else None))
+        return e.value if want_error else None
+
+    def train_step_dev(self, lens, T, inputs_dev, targets_dev, lr, momentum):
+        lens = self._lens(lens)
+        _check(lib().b2_net_train_step_dev(self.h, T, len(lens), lens.ctypes.data, _dev(inputs_dev), _dev(targets_dev),
+                                           lr, momentum))
+
+    def _vec(self, fn, i):
+        out = np.empty((self.T, self.P, self.layers[i]["size"]), np.float32)
+        _check(fn(self.h, i, out.ctypes.data))
+        return out
+
+    def outputs(self, i):
+        return self._vec(lib().b2_net_get_outputs, i)
+
+    def output_errors(self, i):
+        return self._vec(lib().b2_net_get_output_errors, i)
+
+    def synchronize(self):
+        _check(lib().b2_net_synchronize(self.h))
+
+    @property
+    def stream(self):
+        return lib().b2_net_stream(self.h)
+
+    def set_recurrence_mode(self, mode):
+        _check(lib().b2_net_set_recurrence_mode(self.h, mode))
+
+    def set_force_ffma(self, on):
+        _check(lib().b2_net_set_force_ffma(self.h, int(on)))
+
+    @property
+    def launch_count(self):
+        return int(lib().b2_net_launch_count(self.h))
+
+    def set_profiling(self, on):
+        _check(lib().b2_net_set_profiling(self.h, int(on)))
+
+    def get_profile(self):
+        """{phase name: (milliseconds, launches)} accumulated since profiling was switched on; clears."""
+        cap = 64
+        names = (C.c_char_p * cap)()
+        ms = (C.c_float * cap)()
+        ln = (C.c_int * cap)()
+        n = lib().b2_net_get_profile(self.h, cap, names, ms, ln)
+        return {names[i].decode(): (float(ms[i]), int(ln[i])) for i in range(n)}
+
+    def dp_attach(self, rank, world, unique_id):
+        _check(lib().b2_dp_attach(self.h, rank, world, unique_id))
+
+    def dp_detach(self):
+        _check(lib().b2_dp_detach(self.h))
+
+    def dp_allreduce_scalar(self, v):
+        d = C.c_double(v)
+        _check(lib().b2_dp_allreduce_scalar(self.h, C.byref(d)))
+        return d.value

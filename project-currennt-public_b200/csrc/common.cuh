@@ -1,0 +1,112 @@
+// Shared declarations of the b2lstm library: status handling, the activation functions of the
+// reference toolkit as device code, and the launch prototypes of every kernel family.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/b2lstm.h"
+
+namespace b2 {
+
+// ---- status -------------------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what, const char *file, int line);
+#define B2_CUDA(call)                                                              \
+    do {                                                                           \
+        cudaError_t e__ = (call);                                                  \
+        if (e__ != cudaSuccess) return ::b2::cuda_fail(e__, #call, __FILE__, __LINE__); \
+    } while (0)
+#define B2_TRY(call)                  \
+    do {                              \
+        int rc__ = (call);            \
+        if (rc__ != B2_OK) return rc__; \
+    } while (0)
+
+// every kernel launch of the library goes through this counter (b2_net_launch_count)
+extern unsigned long long g_launches;
+inline void count_launch(int n = 1) { g_launches += (unsigned long long)n; }
+
+// ---- activation functions ---------------------------------------------------------------------
+// Same formulas and cut-offs as activation_functions/{Logistic,Tanh,Maxmin1}.cuh of the
+// reference: logistic saturates exactly at |x| >= 88.722839, tanh(x) = 2*logistic(2x) - 1.
+// expf (not __expf) keeps the result within 1-2 ulp of the host libm the reference's Cpu
+// device uses.
+__device__ __forceinline__ float act_logistic(float x) {
+    const float lim = 88.722839f;
+    if (x < lim) {
+        if (x > -lim) return 1.0f / (1.0f + expf(-x));
+        return 0.0f;
+    }
+    return 1.0f;
+}
+__device__ __forceinline__ float d_logistic(float y) { return y * (1.0f - y); }
+__device__ __forceinline__ float act_tanh(float x) { return 2.0f * act_logistic(2.0f * x) - 1.0f; }
+__device__ __forceinline__ float d_tanh(float y) { return 1.0f - y * y; }
+// helpers/limitedError.cuh: clip to [-1, 1]
+__device__ __forceinline__ float limited_error(float e) { return e < -1.0f ? -1.0f : (e > 1.0f ? 1.0f : e); }
+
+enum Act { ACT_TANH = 0, ACT_LOGISTIC = 1, ACT_IDENTITY = 2 };
+enum { PAT_NONE = 0 };
+
+// ---- GEMM family (gemm_ffma.cu, gemm_tc.cu) -------------------------------------------------------
+// C(m x n, column-major, ldc) = A' B' (+ C).  A'(i,k) = A[i*sam + k*sak], B'(k,j) = B[k*sbk + j*sbn].
+// `ws` is split-K scratch of at least ws_floats floats (may be NULL: then no split).
+int gemm_ffma(float *C, long ldc, const float *A, long sam, long sak, const float *B, long sbk, long sbn, int m,
+              int n, int k, bool accumulate, float *ws, size_t ws_floats, cudaStream_t st);
+
+// ---- feed-forward / loss / optimizer elementwise kernels (elementwise.cu) -------------------------
+// y[f*ls + u] = act(y + bias*b[u]) over n = frames*ls elements
+int ff_bias_act(float *y, const float *b, float bias, int ls, size_t n, int act, cudaStream_t st);
+// delta[i] = act'(y[i]) * err[i], in place on err
+int ff_delta(float *err, const float *y, size_t n, int act, cudaStream_t st);
+// out[u] = scale * sum_f m[f*ld + u], u < cols, f < rows; deterministic two-stage reduction
+int column_sums(float *out, const float *m, long ld, int cols, long rows, float scale, float *ws, size_t ws_floats,
+                cudaStream_t st);
+// SSE: err_partial -> *loss_dev (double) = 0.5*sum (t-y)^2 over non-padding frames
+int sse_loss(double *loss_dev, const float *y, const float *tgt, const char *pat, int ls, size_t frames, double *ws,
+             cudaStream_t st);
+// dy = y - t on real frames, 0 on padding
+int sse_grad(float *dy, const float *y, const float *tgt, const char *pat, int ls, size_t frames, cudaStream_t st);
+// steepest descent with momentum; zeroes NaN/Inf gradient entries first
+int sgd_update(float *w, float *g, float *delta, size_t n, float lr, float mom, cudaStream_t st);
+int fill_zero(void *p, size_t bytes, cudaStream_t st);
+
+// ---- LSTM recurrence (lstm_step.cu, lstm_persistent.cu) -------------------------------------------
+struct LstmShape {
+    int P, T, Tmin, pls, ls, els, D;  // D = directions (1 or 2)
+    float bias;
+};
+struct LstmBuffers {
+    float *acts;        // [T*P][4*ls]: pre-activations from the input projection, overwritten by the
+                        //              post-activation ni, ig, fg, og; column c = g*ls + dir*els + j
+    float *cells;       // [T*P][ls]:   cell states, column dir*els + j
+    float *deltas;      // [T*P][4*ls]: gate deltas, same column order as acts
+    float *cerr;        // [2][P][ls]:  cell-state errors of the two most recent steps (stepwise kernels)
+    float *wrecT;       // [D][els][4][els]: recurrent weights, source unit major (forward sweep)
+    const char *pat;    // [T*P]
+};
+// one launch per timestep, both directions in the same launch
+int lstm_forward_stepwise(const LstmShape &s, const LstmBuffers &b, const float *w, float *y, cudaStream_t st);
+int lstm_backward_stepwise(const LstmShape &s, const LstmBuffers &b, const float *w, const float *dy,
+                           cudaStream_t st);
+// transpose the recurrent block of the weight vector into LstmBuffers::wrecT
+int lstm_prepare_wrecT(const LstmShape &s, const float *w, float *wrecT, cudaStream_t st);
+// bias and peephole gradients (the vector part of the weight update), written into dw
+int lstm_vector_grads(const LstmShape &s, const LstmBuffers &b, float *dw, float *ws, size_t ws_floats,
+                      cudaStream_t st);
+
+// offsets inside the (b)lstm weight vector
+struct LstmOffsets {
+    size_t bias, rec, peep, total;
+};
+__host__ __device__ inline LstmOffsets lstm_offsets(int pls, int ls, int els) {
+    LstmOffsets o;
+    o.bias = (size_t)4 * ls * pls;
+    o.rec = o.bias + (size_t)4 * ls;
+    o.peep = o.rec + (size_t)4 * ls * els;
+    o.total = o.peep + (size_t)3 * ls;
+    return o;
+}
+
+}  // namespace b2

@@ -1,0 +1,201 @@
+// HBM-bound elementwise and reduction kernels around the LSTM stack: feed-forward bias +
+// activation and delta, column sums (bias gradients), the SSE objective and its gradient, and the
+// steepest-descent update.  Reference counterparts (paths inside CURRENNT_codes/currennt_lib/src/):
+//   layers/FeedForwardLayer.cu:53-74 (ComputeOutputFn), :106-116 (ComputeDeltaFn),
+//                              :118-138 (ComputeBiasWeightUpdateFn)
+//   layers/SsePostOutputLayer.cu:94-136 (ComputeSseFn, ComputeOutputErrorFn)
+//   optimizers/SteepestDescentOptimizer.cu:74-100 (UpdateWeightFn)
+// Grids are sized in multiples of the 148 SMs and grid-stride over the data with 128-bit accesses
+// where the alignment allows.
+#include "common.cuh"
+
+namespace b2 {
+namespace {
+
+constexpr int SMS = 148;
+
+__device__ __forceinline__ float apply_act(int act, float a) {
+    return act == ACT_TANH ? act_tanh(a) : (act == ACT_LOGISTIC ? act_logistic(a) : a);
+}
+__device__ __forceinline__ float apply_deriv(int act, float y) {
+    return act == ACT_TANH ? d_tanh(y) : (act == ACT_LOGISTIC ? d_logistic(y) : 1.0f);
+}
+
+__global__ void ff_bias_act_kernel(float *__restrict__ y, const float *__restrict__ b, float bias, int ls, size_t n,
+                                   int act) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    if ((ls & 3) == 0) {
+        size_t n4 = n / 4;
+        float4 *y4 = reinterpret_cast<float4 *>(y);
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+            float4 v = y4[i];
+            int u = (int)((i * 4) % ls);
+            v.x = apply_act(act, v.x + bias * __ldg(b + u));
+            v.y = apply_act(act, v.y + bias * __ldg(b + u + 1));
+            v.z = apply_act(act, v.z + bias * __ldg(b + u + 2));
+            v.w = apply_act(act, v.w + bias * __ldg(b + u + 3));
+            y4[i] = v;
+        }
+    } else {
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+            y[i] = apply_act(act, y[i] + bias * __ldg(b + (i % ls)));
+    }
+}
+
+__global__ void ff_delta_kernel(float *__restrict__ err, const float *__restrict__ y, size_t n, int act) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t n4 = n / 4;
+    float4 *e4 = reinterpret_cast<float4 *>(err);
+    const float4 *y4 = reinterpret_cast<const float4 *>(y);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 e = e4[i], v = y4[i];
+        e.x *= apply_deriv(act, v.x); e.y *= apply_deriv(act, v.y);
+        e.z *= apply_deriv(act, v.z); e.w *= apply_deriv(act, v.w);
+        e4[i] = e;
+    }
+    for (size_t i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        err[i] = apply_deriv(act, y[i]) * err[i];
+}
+
+constexpr int CS_ROWS = 512;  // rows (frames) per partial sum
+__global__ void column_sums_partial_kernel(float *__restrict__ ws, const float *__restrict__ m, long ld, int cols,
+                                           long rows) {
+    int u = blockIdx.x * blockDim.x + threadIdx.x;
+    if (u >= cols) return;
+    long r0 = (long)blockIdx.y * CS_ROWS, r1 = min(rows, r0 + CS_ROWS);
+    float s = 0.0f;
+    for (long r = r0; r < r1; ++r) s += m[(size_t)r * ld + u];
+    ws[(size_t)blockIdx.y * cols + u] = s;
+}
+__global__ void column_sums_reduce_kernel(float *__restrict__ out, const float *__restrict__ ws, int cols, int chunks,
+                                          float scale) {
+    int u = blockIdx.x * blockDim.x + threadIdx.x;
+    if (u >= cols) return;
+    float s = 0.0f;
+    for (int c = 0; c < chunks; ++c) s += ws[(size_t)c * cols + u];
+    out[u] = scale * s;
+}
+
+__global__ void sse_partial_kernel(double *__restrict__ ws, const float *__restrict__ y, const float *__restrict__ tgt,
+                                   const char *__restrict__ pat, int ls, size_t n) {
+    float s = 0.0f;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        if (pat[i / ls] == PAT_NONE) continue;
+        float d = tgt[i] - y[i];
+        s = fmaf(d, d, s);
+    }
+    double v = (double)s;
+    __shared__ double red[32];
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0;
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+        if (threadIdx.x == 0) ws[blockIdx.x] = v;
+    }
+}
+__global__ void sse_final_kernel(double *__restrict__ loss, const double *__restrict__ ws, int blocks) {
+    double v = 0.0;
+    for (int i = threadIdx.x; i < blocks; i += 32) v += ws[i];
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+    if (threadIdx.x == 0) *loss = 0.5 * v;
+}
+
+__global__ void sse_grad_kernel(float *__restrict__ dy, const float *__restrict__ y, const float *__restrict__ tgt,
+                                const char *__restrict__ pat, int ls, size_t n) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        dy[i] = pat[i / ls] == PAT_NONE ? 0.0f : y[i] - tgt[i];
+}
+
+__global__ void sgd_update_kernel(float *__restrict__ w, float *__restrict__ g, float *__restrict__ delta, size_t n,
+                                  float lr, float mom) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float gi = g[i];
+        if (isnan(gi) || isinf(gi)) { gi = 0.0f; g[i] = 0.0f; }
+        float dl = mom * delta[i] - lr * gi;
+        delta[i] = dl;
+        w[i] = w[i] + dl;
+    }
+}
+
+inline int grid_for(size_t n, int threads, int per_sm = 8) {
+    size_t b = (n + threads - 1) / threads;
+    size_t cap = (size_t)SMS * per_sm;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+}  // namespace
+
+int fill_zero(void *p, size_t bytes, cudaStream_t st) {
+    if (!bytes) return B2_OK;
+    B2_CUDA(cudaMemsetAsync(p, 0, bytes, st));
+    return B2_OK;
+}
+
+int ff_bias_act(float *y, const float *b, float bias, int ls, size_t n, int act, cudaStream_t st) {
+    if (!n) return B2_OK;
+    ff_bias_act_kernel<<<grid_for(n / 4 + 1, 256), 256, 0, st>>>(y, b, bias, ls, n, act);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int ff_delta(float *err, const float *y, size_t n, int act, cudaStream_t st) {
+    if (!n || act == ACT_IDENTITY) return B2_OK;  // identity: deriv = 1, delta = err unchanged
+    ff_delta_kernel<<<grid_for(n / 4 + 1, 256), 256, 0, st>>>(err, y, n, act);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int column_sums(float *out, const float *m, long ld, int cols, long rows, float scale, float *ws, size_t ws_floats,
+                cudaStream_t st) {
+    int chunks = (int)((rows + CS_ROWS - 1) / CS_ROWS);
+    if (chunks < 1) chunks = 1;
+    if ((size_t)chunks * cols > ws_floats) {
+        set_error("column_sums: scratch too small");
+        return B2_ERR_BAD_SHAPE;
+    }
+    dim3 grid((cols + 127) / 128, chunks);
+    column_sums_partial_kernel<<<grid, 128, 0, st>>>(ws, m, ld, cols, rows);
+    column_sums_reduce_kernel<<<(cols + 127) / 128, 128, 0, st>>>(out, ws, cols, chunks, scale);
+    count_launch(2);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int sse_loss(double *loss_dev, const float *y, const float *tgt, const char *pat, int ls, size_t frames, double *ws,
+             cudaStream_t st) {
+    size_t n = frames * (size_t)ls;
+    int blocks = grid_for(n, 256, 4);  // <= 592 partials; ws holds 1024 doubles
+    sse_partial_kernel<<<blocks, 256, 0, st>>>(ws, y, tgt, pat, ls, n);
+    sse_final_kernel<<<1, 32, 0, st>>>(loss_dev, ws, blocks);
+    count_launch(2);
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int sse_grad(float *dy, const float *y, const float *tgt, const char *pat, int ls, size_t frames, cudaStream_t st) {
+    size_t n = frames * (size_t)ls;
+    if (!n) return B2_OK;
+    sse_grad_kernel<<<grid_for(n, 256), 256, 0, st>>>(dy, y, tgt, pat, ls, n);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int sgd_update(float *w, float *g, float *delta, size_t n, float lr, float mom, cudaStream_t st) {
+    if (!n) return B2_OK;
+    sgd_update_kernel<<<grid_for(n, 256), 256, 0, st>>>(w, g, delta, n, lr, mom);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+}  // namespace b2

@@ -1,0 +1,202 @@
+// b2_lstm: one peephole (B)LSTM layer working on the caller's buffers -- the C-ABI stand-in for
+// layers::LstmLayer<Gpu> of the reference (layers/LstmLayer.hpp:168-308, LstmLayer.cu:1079-2382).
+//
+// Data layout in HBM (frames f = t*P + p, all fp32, column-major with the frame as column):
+//   acts   [4*ls x T*P]  row c = g*ls + dir*els + j; written once by the fused input projection
+//                        (all four gates, both directions = ONE GEMM, M = 4*ls), then overwritten
+//                        in place by the recurrence with the post-activation ni, ig, fg, og
+//   cells  [ls x T*P]    cell states, row dir*els + j
+//   deltas [4*ls x T*P]  gate deltas, same rows as acts; operand of the dX and dW GEMMs
+//   y      [ls x T*P]    block outputs straight in the caller's outputs() vector, forward units
+//                        first (no separate per-direction copy, no resort pass)
+// The reference keeps 12 vectors of T*P*els per direction (LstmLayer.cu:1184-1209); this keeps
+// 9*ls floats per frame against its 12*ls (+2*ls for outputs and errors on both sides).
+#include <new>
+
+#include "common.cuh"
+#include "lstm_layer.hpp"
+
+namespace b2 {
+
+namespace {
+struct Phase {
+    LstmLayerImpl &l;
+    Phase(LstmLayerImpl &layer, const char *name) : l(layer) { if (l.prof_begin) l.prof_begin(l.prof_ctx, name); }
+    ~Phase() { if (l.prof_end) l.prof_end(l.prof_ctx); }
+};
+}  // namespace
+
+int LstmLayerImpl::create(const b2_lstm_desc &d) {
+    desc = d;
+    D = d.bidirectional ? 2 : 1;
+    if (d.size <= 0 || d.prev_size <= 0 || d.parallel_sequences <= 0 || d.max_seq_length <= 0 ||
+        (d.bidirectional && (d.size & 1))) {
+        set_error("b2_lstm_create: bad descriptor (size %d prev %d P %d maxT %d bidirectional %d)", d.size,
+                  d.prev_size, d.parallel_sequences, d.max_seq_length, d.bidirectional);
+        return B2_ERR_BAD_SHAPE;
+    }
+    els = d.size / D;
+    size_t frames = (size_t)d.max_seq_length * d.parallel_sequences;
+    size_t ls = d.size;
+    B2_CUDA(cudaMalloc(&bufs.acts, frames * 4 * ls * sizeof(float)));
+    B2_CUDA(cudaMalloc(&bufs.cells, frames * ls * sizeof(float)));
+    B2_CUDA(cudaMalloc(&bufs.deltas, frames * 4 * ls * sizeof(float)));
+    B2_CUDA(cudaMalloc(&bufs.cerr, (size_t)2 * d.parallel_sequences * ls * sizeof(float)));
+    B2_CUDA(cudaMalloc(&bufs.wrecT, (size_t)D * 4 * els * els * sizeof(float)));
+    size_t vg = ((frames + 255) / 256) * 7 * ls;
+    ws_floats = vg > ((size_t)6 << 20) ? vg : ((size_t)6 << 20);
+    B2_CUDA(cudaMalloc(&ws, ws_floats * sizeof(float)));
+    state_bytes = (frames * 9 * ls + (size_t)2 * d.parallel_sequences * ls + (size_t)D * 4 * els * els + ws_floats) *
+                  sizeof(float);
+    // padding frames beyond the current fraction are never read, but start from defined memory
+    B2_CUDA(cudaMemset(bufs.acts, 0, frames * 4 * ls * sizeof(float)));
+    B2_CUDA(cudaMemset(bufs.cells, 0, frames * ls * sizeof(float)));
+    B2_CUDA(cudaMemset(bufs.deltas, 0, frames * 4 * ls * sizeof(float)));
+    return B2_OK;
+}
+
+void LstmLayerImpl::destroy() {
+    cudaFree(bufs.acts); cudaFree(bufs.cells); cudaFree(bufs.deltas); cudaFree(bufs.cerr); cudaFree(bufs.wrecT);
+    cudaFree(ws);
+    bufs = LstmBuffers();
+    ws = nullptr;
+}
+
+LstmShape LstmLayerImpl::shape() const {
+    LstmShape s;
+    s.P = desc.parallel_sequences; s.T = T; s.Tmin = Tmin; s.pls = desc.prev_size; s.ls = desc.size;
+    s.els = els; s.D = D; s.bias = desc.bias;
+    return s;
+}
+
+int LstmLayerImpl::load_sequences(int cur_max, int cur_min, const char *pat) {
+    if (cur_max <= 0 || cur_max > desc.max_seq_length || cur_min < 0 || cur_min > cur_max || !pat) {
+        set_error("b2_lstm_load_sequences: lengths %d/%d outside 1..%d", cur_max, cur_min, desc.max_seq_length);
+        return B2_ERR_BAD_SHAPE;
+    }
+    T = cur_max; Tmin = cur_min; bufs.pat = pat;
+    forward_done = false;
+    return B2_OK;
+}
+
+int LstmLayerImpl::forward(const float *w, const float *x, float *y, cudaStream_t st) {
+    if (!T) { set_error("b2_lstm_forward: no sequences loaded"); return B2_ERR_STATE; }
+    if (!w || !x || !y) { set_error("b2_lstm_forward: null pointer"); return B2_ERR_BAD_ARG; }
+    const LstmShape s = shape();
+    const int N = s.T * s.P, ls = s.ls, pls = s.pls;
+    // input projection for all gates and both directions (reference: 4*D cublasSgemm calls,
+    // LstmLayer.cu:1756-1775): acts(4ls x N) = W_in^T X, W_in viewed as ONE pls x 4ls matrix
+    {
+        Phase ph(*this, "lstm_proj_gemm");
+        B2_TRY(gemm(bufs.acts, 4 * ls, w, pls, 1, x, 1, pls, 4 * ls, N, pls, false, st));
+    }
+    {
+        Phase ph(*this, "lstm_fwd_recurrence");
+        B2_TRY(lstm_prepare_wrecT(s, w, bufs.wrecT, st));
+        B2_TRY(lstm_forward_stepwise(s, bufs, w, y, st));
+    }
+    forward_done = true;
+    return B2_OK;
+}
+
+int LstmLayerImpl::backward(const float *w, const float *x, const float *y, const float *dy, float *dx, float *dw,
+                            cudaStream_t st) {
+    if (!forward_done) { set_error("b2_lstm_backward: forward pass of this fraction has not run"); return B2_ERR_STATE; }
+    if (!w || !x || !y || !dy || !dw) { set_error("b2_lstm_backward: null pointer"); return B2_ERR_BAD_ARG; }
+    const LstmShape s = shape();
+    const int N = s.T * s.P, ls = s.ls, pls = s.pls, P = s.P;
+    const LstmOffsets off = lstm_offsets(pls, ls, els);
+    {
+        Phase ph(*this, "lstm_bwd_recurrence");
+        B2_TRY(lstm_backward_stepwise(s, bufs, w, dy, st));
+    }
+    // error to the preceding layer (reference: 4*D Sgemm, LstmLayer.cu:2298-2334): dX = W_in * deltas
+    if (dx) {
+        Phase ph(*this, "lstm_dx_gemm");
+        B2_TRY(gemm(dx, pls, w, 1, pls, bufs.deltas, 1, 4 * ls, pls, N, 4 * ls, false, st));
+    }
+    // input weight gradients (reference: one thread per weight, serial over frames,
+    // LstmLayer.cu:490-522): dW_in(pls x 4ls) = X * deltas^T, written straight into the weight layout
+    {
+        Phase ph(*this, "lstm_dw_in_gemm");
+        B2_TRY(gemm(dw, pls, x, 1, pls, bufs.deltas, 4 * ls, 1, pls, 4 * ls, N, false, st));
+    }
+    // recurrent weight gradients (LstmLayer.cu:543-572,629-636): for gate g, direction d
+    //   dW_rec[g][d](k, j) = sum_f h_d[k; f -/+ P] * delta_g,d[j; f], skipping the first (last) timestep
+    const int K = N - P;
+    {
+    Phase ph(*this, "lstm_dw_rec_gemm");
+    for (int d = 0; d < D; ++d)
+        for (int g = 0; g < 4; ++g) {
+            float *C = dw + off.rec + ((size_t)g * ls + (size_t)d * els) * els;
+            const float *A = y + (size_t)d * els + (d ? (size_t)P * ls : 0);
+            const float *B = bufs.deltas + (size_t)g * ls + (size_t)d * els + (d ? 0 : (size_t)P * 4 * ls);
+            B2_TRY(gemm(C, els, A, 1, ls, B, 4 * ls, 1, els, els, K, false, st));
+        }
+    }
+    Phase ph(*this, "lstm_vector_grads");
+    B2_TRY(lstm_vector_grads(s, bufs, dw, ws, ws_floats, st));
+    return B2_OK;
+}
+
+int LstmLayerImpl::gemm(float *C, long ldc, const float *A, long sam, long sak, const float *B, long sbk, long sbn,
+                        int m, int n, int k, bool acc, cudaStream_t st) {
+    return gemm_ffma(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, acc, ws, ws_floats, st);
+}
+
+}  // namespace b2
+
+using b2::LstmLayerImpl;
+struct b2_lstm {
+    LstmLayerImpl impl;
+};
+
+extern "C" {
+
+size_t b2_lstm_num_weights(const b2_lstm_desc *d) {
+    if (!d) return 0;
+    size_t ls = d->size, pls = d->prev_size, els = d->bidirectional ? ls / 2 : ls;
+    return ls * (4 * (pls + 1) + 4 * els + 3);
+}
+
+int b2_lstm_create(const b2_lstm_desc *desc, b2_lstm **out) {
+    if (!desc || !out) { b2::set_error("b2_lstm_create: null argument"); return B2_ERR_BAD_ARG; }
+    b2_lstm *l = new (std::nothrow) b2_lstm;
+    if (!l) return B2_ERR_BAD_ARG;
+    int rc = l->impl.create(*desc);
+    if (rc != B2_OK) { l->impl.destroy(); delete l; return rc; }
+    *out = l;
+    return B2_OK;
+}
+
+void b2_lstm_destroy(b2_lstm *l) {
+    if (!l) return;
+    l->impl.destroy();
+    delete l;
+}
+
+int b2_lstm_load_sequences(b2_lstm *l, int cur_max_len, int cur_min_len, const char *pat_types_dev) {
+    if (!l) return B2_ERR_BAD_ARG;
+    return l->impl.load_sequences(cur_max_len, cur_min_len, pat_types_dev);
+}
+
+int b2_lstm_forward(b2_lstm *l, const float *w, const float *x, float *y, b2_stream st) {
+    if (!l) return B2_ERR_BAD_ARG;
+    return l->impl.forward(w, x, y, (cudaStream_t)st);
+}
+
+int b2_lstm_backward(b2_lstm *l, const float *w, const float *x, const float *y, const float *dy, float *dx,
+                     float *dw, b2_stream st) {
+    if (!l) return B2_ERR_BAD_ARG;
+    return l->impl.backward(w, x, y, dy, dx, dw, (cudaStream_t)st);
+}
+
+int b2_lstm_set_recurrence_mode(b2_lstm *l, int mode) {
+    if (!l) return B2_ERR_BAD_ARG;
+    l->impl.recurrence_mode = mode;
+    return B2_OK;
+}
+
+size_t b2_lstm_state_bytes(const b2_lstm *l) { return l ? l->impl.state_bytes : 0; }
+
+}  // extern "C"

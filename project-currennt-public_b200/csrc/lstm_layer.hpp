@@ -1,0 +1,34 @@
+// Implementation object behind the opaque b2_lstm handle; also used directly by the layer stack.
+#pragma once
+#include "common.cuh"
+
+namespace b2 {
+
+struct LstmLayerImpl {
+    b2_lstm_desc desc{};
+    int D = 1, els = 0;
+    int T = 0, Tmin = 0;
+    bool forward_done = false;
+    int recurrence_mode = 1;   // 0 stepwise, 1 persistent
+    bool force_ffma = false;
+    LstmBuffers bufs{};
+    float *ws = nullptr;       // scratch: split-K partials, vector-gradient partials
+    size_t ws_floats = 0;
+    size_t state_bytes = 0;
+    // optional per-phase timing hooks (set by the layer stack when profiling is on)
+    void *prof_ctx = nullptr;
+    void (*prof_begin)(void *, const char *) = nullptr;
+    void (*prof_end)(void *) = nullptr;
+
+    int create(const b2_lstm_desc &d);
+    void destroy();
+    LstmShape shape() const;
+    int load_sequences(int cur_max, int cur_min, const char *pat_dev);
+    int forward(const float *w, const float *x, float *y, cudaStream_t st);
+    int backward(const float *w, const float *x, const float *y, const float *dy, float *dx, float *dw,
+                 cudaStream_t st);
+    int gemm(float *C, long ldc, const float *A, long sam, long sak, const float *B, long sbk, long sbn, int m, int n,
+             int k, bool acc, cudaStream_t st);
+};
+
+}  // namespace b2

@@ -1,0 +1,215 @@
+"""GPU parity tests: the CUDA path, called through the C ABI (ctypes), against
+(1) the golden tensors produced by the reference's own Cpu code,
+(2) the checker on fresh seeded inputs: the compiled reference where it travelled with the
+    repository, otherwise the C restatement that the CPU tests pin to it,
+for every recurrence / GEMM variant the library offers."""
+import numpy as np
+import pytest
+
+import parity
+from make_golden import run as run_kind
+from oracle import ref_available
+
+pytestmark = pytest.mark.gpu
+
+VARIANTS = [dict(recurrence=0, ffma=1), dict(recurrence=1, ffma=1), dict(recurrence=1, ffma=0), dict(recurrence=0, ffma=0)]
+VARIANT_IDS = ["stepwise-ffma", "persistent-ffma", "persistent-tensor", "stepwise-tensor"]
+
+
+def run_gpu(layers, P, lens, x, tg, weights, variant, lr=1e-4, mom=0.9, maxT=None):
+    import b2lstm
+    net = b2lstm.Net(layers, P, maxT or x.shape[0])
+    net.set_recurrence_mode(variant["recurrence"])
+    net.set_force_ffma(variant["ffma"])
+    for i, w in weights.items():
+        net.set_weights(i, w)
+    net.load_fraction(lens, x, tg)
+    out = {"loss": net.forward()}
+    for i in range(1, len(layers)):
+        if layers[i]["type"] != "sse":
+            out["out%d" % i] = net.outputs(i)
+    net.backward()
+    for i in range(1, len(layers)):
+        # what a layer received as output errors: a feed-forward layer turns them into deltas in
+        # place (as the reference does), an lstm layer leaves them untouched -> compare lstm inputs
+        if layers[i]["type"] in ("lstm", "blstm"):
+            out["dyin%d" % i] = net.output_errors(i)
+        if i in weights:
+            out["dw%d" % i] = net.weight_updates(i)
+    net.update_weights(lr, mom)
+    net.synchronize()
+    for i in weights:
+        out["wnew%d" % i] = net.get_weights(i)
+    out["launches"] = net.launch_count
+    net.close()
+    return out
+
+
+@pytest.mark.parametrize("variant", VARIANTS, ids=VARIANT_IDS)
+@pytest.mark.parametrize("name", parity.golden_cases())
+def test_golden(name, variant):
+    g = parity.load_golden(name)
+    got = run_gpu(g["layers"], g["P"], g["lens"], g["x"], g["tg"], g["weights"], variant)
+    assert got["launches"] > 0
+    parity.compare_run(g["layers"], got, g, name, lstm_pad_zero_lens=g["lens"])
+    for i in g["weights"]:
+        parity.assert_rel_close(got["wnew%d" % i] - g["w%d" % i], g["wnew%d" % i] - g["w%d" % i],
+                                "%s weight step of layer %d" % (name, i))
+
+
+def checker():
+    return "ref" if ref_available() else "port"
+
+
+def L(*spec):
+    return [dict(type=t, size=s, **({} if t in ("input", "sse") else {"bias": 1.0})) for t, s in spec]
+
+
+SHAPES = []
+for els in (1, 3, 32, 33):
+    for P in (1, 3):
+        for T in (1, 2, 5):
+            for bi in (0, 1):
+                SHAPES.append((els, P, T, bi))
+
+
+@pytest.mark.parametrize("variant", VARIANTS[:3], ids=VARIANT_IDS[:3])
+def test_small_shapes_exhaustive(variant):
+    """els in {1,3,32,33} x P in {1,3} x T in {1,2,5} x uni/bi, ragged lengths, run twice (determinism)."""
+    from b2lstm import workloads
+    for k, (els, P, T, bi) in enumerate(SHAPES):
+        ls = els * (2 if bi else 1)
+        layers = L(("input", 5), ("blstm" if bi else "lstm", ls), ("feedforward_identity", 3), ("sse", 3))
+        lens = np.array([T] + [max(1, T - 1 - p) for p in range(P - 1)], np.int32)
+        x, tg = workloads.make_fraction(5, 3, P, lens, 500 + k, 600 + k)
+        w = workloads.make_weights(layers, 700 + k, 0.3)
+        want = run_kind(checker(), layers, P, lens, x, tg, w)
+        got = run_gpu(layers, P, lens, x, tg, w, variant)
+        parity.compare_run(layers, got, want, "els%d P%d T%d bi%d" % (els, P, T, bi), lstm_pad_zero_lens=lens)
+        again = run_gpu(layers, P, lens, x, tg, w, variant)
+        for key in got:
+            if key != "launches":
+                assert np.array_equal(np.asarray(got[key]), np.asarray(again[key])), "not deterministic: " + key
+
+
+@pytest.mark.parametrize("variant", VARIANTS[:3], ids=VARIANT_IDS[:3])
+def test_cfg0_full(variant):
+    """Configuration 0 at full size: 64 -> lstm 128 -> ff 32 -> sse, 4 x 200 frames."""
+    from b2lstm import workloads
+    wl = workloads.build(0)
+    want = run_kind(checker(), wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"])
+    got = run_gpu(wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"], variant)
+    parity.compare_run(wl["layers"], got, want, "cfg0")
+
+
+@pytest.mark.parametrize("variant", VARIANTS[1:3], ids=VARIANT_IDS[1:3])
+@pytest.mark.parametrize("cfg,P,scale", [(1, 6, 0.04), (3, 1, 0.01), (4, 5, 0.03)])
+def test_config_layer_sizes_reduced_frames(cfg, P, scale, variant):
+    """Configurations 1, 3, 4 with their real layer sizes on a reduced frame budget (the checker is
+    a serial CPU program): ragged lengths, padding, both directions, 256/512-unit recurrences."""
+    from b2lstm import workloads
+    wl = workloads.build(cfg, scale_frames=scale, P=P)
+    want = run_kind(checker(), wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"])
+    got = run_gpu(wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"], variant)
+    parity.compare_run(wl["layers"], got, want, "cfg%d reduced" % cfg, lstm_pad_zero_lens=wl["lens"])
+
+
+def test_reuse_across_fractions_of_different_length():
+    """A net sized for the longest fraction processes shorter and longer fractions back to back
+    (stale state in the buffers must not leak into the next fraction)."""
+    import b2lstm
+    from b2lstm import workloads
+    layers = L(("input", 6), ("blstm", 20), ("lstm", 7), ("feedforward_identity", 3), ("sse", 3))
+    P = 4
+    w = workloads.make_weights(layers, 42, 0.2)
+    net = b2lstm.Net(layers, P, 30)
+    for i, wi in w.items():
+        net.set_weights(i, wi)
+    for k, lens in enumerate([[30, 22, 30, 4], [7, 7, 3], [19], [30, 30, 30, 30]]):
+        lens = np.array(lens, np.int32)
+        x, tg = workloads.make_fraction(6, 3, P, lens, 900 + k, 950 + k)
+        want = run_kind(checker(), layers, P, lens, x, tg, w)
+        net.load_fraction(lens, x, tg)
+        got = {"loss": net.forward()}
+        net.backward()
+        for i in (1, 2, 3):
+            got["out%d" % i] = net.outputs(i)
+            got["dw%d" % i] = net.weight_updates(i)
+        parity.compare_run(layers, got, want, "fraction %d" % k, lstm_pad_zero_lens=lens)
+    net.close()
+
+
+def test_layer_level_entry_points_on_caller_buffers():
+    """b2_lstm_* on torch-owned device buffers, the drop-in for layers::LstmLayer<Gpu>."""
+    import torch
+    import b2lstm
+    from b2lstm import workloads
+    P, T, pls, ls = 3, 9, 6, 10
+    layers = L(("input", pls), ("blstm", ls), ("feedforward_identity", 4), ("sse", 4))
+    lens = np.array([9, 5, 9], np.int32)
+    x, tg = workloads.make_fraction(pls, 4, P, lens, 11, 12)
+    w = workloads.make_weights(layers, 13, 0.3)
+    want = run_kind(checker(), layers, P, lens, x, tg, w)
+    dev = torch.device("cuda:0")
+    pat = np.zeros((T, P), np.int8)
+    for p, n in enumerate(lens):
+        pat[:n, p] = 2
+        pat[0, p] = 1
+        pat[n - 1, p] = 3
+    layer = b2lstm.LstmLayer(P, T, pls, ls, True, 1.0)
+    assert layer.num_weights == w[1].size
+    tw, tx = torch.from_numpy(w[1]).to(dev), torch.from_numpy(x).to(dev)
+    tpat = torch.from_numpy(pat).to(dev)
+    ty = torch.full((T, P, ls), float("nan"), device=dev)
+    layer.load_sequences(T, int(lens.min()), tpat)
+    layer.forward(tw, tx, ty)
+    torch.cuda.synchronize()
+    parity.assert_outputs_close(ty.cpu().numpy(), want["out1"], "layer-level outputs")
+    tdy = torch.from_numpy(want["dyin1"]).to(dev)
+    tdx = torch.full((T, P, pls), float("nan"), device=dev)
+    tdw = torch.full((layer.num_weights,), float("nan"), device=dev)
+    layer.backward(tw, tx, ty, tdy, tdx, tdw)
+    torch.cuda.synchronize()
+    parity.assert_grads_close(layers, 1, tdw.cpu().numpy(), want["dw1"], "layer-level")
+    assert np.isfinite(tdx.cpu().numpy()).all()
+    layer.close()
+
+
+def test_matrix_multiply_wrapper():
+    """b2_matrix_multiply = helpers::Matrix::assignProduct/addProduct, every transpose the reference
+    supports, ragged sizes, against float64 numpy."""
+    import torch
+    import b2lstm
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(5)
+    for (m, n, k) in [(1, 1, 1), (7, 5, 3), (128, 128, 64), (130, 70, 257), (64, 512, 800), (384, 96, 4100)]:
+        for ta, tb in [(0, 0), (1, 0), (0, 1)]:
+            for ffma in (1, 0):
+                A = rng.standard_normal((k, m) if not ta else (m, k)).astype(np.float32)   # stored column-major
+                B = rng.standard_normal((n, k) if not tb else (k, n)).astype(np.float32)
+                C0 = rng.standard_normal((n, m)).astype(np.float32)
+                opA = A.T.astype(np.float64) if not ta else A.astype(np.float64)          # m x k
+                opB = B.T.astype(np.float64) if not tb else B.astype(np.float64)          # k x n
+                want = opA @ opB
+                tA, tB, tC = torch.from_numpy(A).to(dev), torch.from_numpy(B).to(dev), torch.from_numpy(C0).to(dev)
+                lda = m if not ta else k
+                ldb = k if not tb else n
+                b2lstm.matrix_multiply(tC, m, tA, lda, ta, tB, ldb, tb, m, n, k, accumulate=False, force_ffma=ffma)
+                torch.cuda.synchronize()
+                got = tC.cpu().numpy().T
+                scale = np.sqrt(k)
+                assert np.abs(got - want).max() <= 2e-6 * scale * 8, (m, n, k, ta, tb, ffma, np.abs(got - want).max())
+                b2lstm.matrix_multiply(tC, m, tA, lda, ta, tB, ldb, tb, m, n, k, accumulate=True, force_ffma=ffma)
+                torch.cuda.synchronize()
+                assert np.abs(tC.cpu().numpy().T - 2 * want).max() <= 4e-6 * scale * 8
+
+
+def test_errors_are_status_codes():
+    import b2lstm
+    layers = L(("input", 4), ("lstm", 4), ("sse", 4))
+    net = b2lstm.Net(layers, 2, 5)
+    with pytest.raises(b2lstm.B2Error):
+        net.forward()                       # nothing loaded
+    with pytest.raises(b2lstm.B2Error):
+        net.load_fraction(np.array([9], np.int32), np.zeros((9, 2, 4), np.float32), np.zeros((9, 2, 4), np.float32))
+    net.close()
