@@ -96,6 +96,9 @@ int b2_lstm_backward(b2_lstm *layer, const float *weights_dev, const float *x_de
                      const float *dy_dev, float *dx_dev, float *dw_dev, b2_stream stream);
 /* Which recurrence kernels run: 0 = one launch per timestep, 1 = persistent kernel (default). */
 int b2_lstm_set_recurrence_mode(b2_lstm *layer, int mode);
+/* Waits for the work enqueued on `stream` and reports what the layer's kernels recorded:
+ * B2_ERR_STEP_TIMEOUT if a persistent kernel gave up a bounded wait, else B2_OK. */
+int b2_lstm_synchronize(b2_lstm *layer, b2_stream stream);
 /* Bytes of private device memory the layer holds. */
 size_t b2_lstm_state_bytes(const b2_lstm *layer);
 

@@ -39,6 +39,7 @@ SIGNATURES = {
     "b2_lstm_backward": (C.c_int, [C.c_void_p] * 8),
     "b2_lstm_set_recurrence_mode": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_lstm_state_bytes": (C.c_size_t, [C.c_void_p]),
+    "b2_lstm_synchronize": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b2_net_create": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_uint, C.POINTER(C.c_void_p)]),
     "b2_net_destroy": (None, [C.c_void_p]),
     "b2_net_num_layers": (C.c_int, [C.c_void_p]),
@@ -154,6 +155,9 @@ class LstmLayer:
 
     def set_recurrence_mode(self, mode):
         _check(lib().b2_lstm_set_recurrence_mode(self.h, mode))
+
+    def synchronize(self, stream=None):
+        _check(lib().b2_lstm_synchronize(self.h, stream))
 
     @property
     def state_bytes(self):

@@ -96,6 +96,12 @@ int lstm_prepare_wrecT(const LstmShape &s, const float *w, float *wrecT, cudaStr
 int lstm_vector_grads(const LstmShape &s, const LstmBuffers &b, float *dw, float *ws, size_t ws_floats,
                       cudaStream_t st);
 
+// persistent kernels (lstm_persistent.cu).  Return B2_OK, an error, or 1 when the shape has no
+// persistent kernel (the caller then uses the stepwise kernels).
+size_t lstm_persistent_xchg_words(int els, int P);
+int lstm_persistent(bool backward, const LstmShape &s, const LstmBuffers &b, const float *w, float *y, const float *dy,
+                    unsigned long long *xchg, int *status, unsigned *tag_next, cudaStream_t st);
+
 // offsets inside the (b)lstm weight vector
 struct LstmOffsets {
     size_t bias, rec, peep, total;

@@ -46,7 +46,14 @@ int LstmLayerImpl::create(const b2_lstm_desc &d) {
     size_t vg = ((frames + 255) / 256) * 7 * ls;
     ws_floats = vg > ((size_t)6 << 20) ? vg : ((size_t)6 << 20);
     B2_CUDA(cudaMalloc(&ws, ws_floats * sizeof(float)));
-    state_bytes = (frames * 9 * ls + (size_t)2 * d.parallel_sequences * ls + (size_t)D * 4 * els * els + ws_floats) *
+    B2_CUDA(cudaMalloc(&status_dev, sizeof(int)));
+    B2_CUDA(cudaMemset(status_dev, 0, sizeof(int)));
+    size_t xw = lstm_persistent_xchg_words(els, d.parallel_sequences);
+    if (xw) {
+        B2_CUDA(cudaMalloc(&xchg, xw * sizeof(unsigned long long)));
+        B2_CUDA(cudaMemset(xchg, 0, xw * sizeof(unsigned long long)));   // tag 0 is never waited for
+    }
+    state_bytes = xw * sizeof(unsigned long long) + (frames * 9 * ls + (size_t)2 * d.parallel_sequences * ls + (size_t)D * 4 * els * els + ws_floats) *
                   sizeof(float);
     // padding frames beyond the current fraction are never read, but start from defined memory
     B2_CUDA(cudaMemset(bufs.acts, 0, frames * 4 * ls * sizeof(float)));
@@ -57,9 +64,9 @@ int LstmLayerImpl::create(const b2_lstm_desc &d) {
 
 void LstmLayerImpl::destroy() {
     cudaFree(bufs.acts); cudaFree(bufs.cells); cudaFree(bufs.deltas); cudaFree(bufs.cerr); cudaFree(bufs.wrecT);
-    cudaFree(ws);
+    cudaFree(ws); cudaFree(xchg); cudaFree(status_dev);
     bufs = LstmBuffers();
-    ws = nullptr;
+    ws = nullptr; xchg = nullptr; status_dev = nullptr;
 }
 
 LstmShape LstmLayerImpl::shape() const {
@@ -93,7 +100,9 @@ int LstmLayerImpl::forward(const float *w, const float *x, float *y, cudaStream_
     {
         Phase ph(*this, "lstm_fwd_recurrence");
         B2_TRY(lstm_prepare_wrecT(s, w, bufs.wrecT, st));
-        B2_TRY(lstm_forward_stepwise(s, bufs, w, y, st));
+        int rc = recurrence_mode == 1 ? lstm_persistent(false, s, bufs, w, y, nullptr, xchg, status_dev, &tag_next, st) : 1;
+        if (rc == 1) rc = lstm_forward_stepwise(s, bufs, w, y, st);
+        B2_TRY(rc);
     }
     forward_done = true;
     return B2_OK;
@@ -108,7 +117,9 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
     const LstmOffsets off = lstm_offsets(pls, ls, els);
     {
         Phase ph(*this, "lstm_bwd_recurrence");
-        B2_TRY(lstm_backward_stepwise(s, bufs, w, dy, st));
+        int rc = recurrence_mode == 1 ? lstm_persistent(true, s, bufs, w, nullptr, dy, xchg, status_dev, &tag_next, st) : 1;
+        if (rc == 1) rc = lstm_backward_stepwise(s, bufs, w, dy, st);
+        B2_TRY(rc);
     }
     // error to the preceding layer (reference: 4*D Sgemm, LstmLayer.cu:2298-2334): dX = W_in * deltas
     if (dx) {
@@ -136,6 +147,18 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
     }
     Phase ph(*this, "lstm_vector_grads");
     B2_TRY(lstm_vector_grads(s, bufs, dw, ws, ws_floats, st));
+    return B2_OK;
+}
+
+int LstmLayerImpl::check_status(cudaStream_t st) {
+    int v = 0;
+    B2_CUDA(cudaMemcpyAsync(&v, status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
+    B2_CUDA(cudaStreamSynchronize(st));
+    if (v != 0) {
+        B2_CUDA(cudaMemsetAsync(status_dev, 0, sizeof(int), st));
+        set_error("a persistent recurrence kernel gave up waiting for a peer block (status %d)", v);
+        return v;
+    }
     return B2_OK;
 }
 
@@ -198,5 +221,10 @@ int b2_lstm_set_recurrence_mode(b2_lstm *l, int mode) {
 }
 
 size_t b2_lstm_state_bytes(const b2_lstm *l) { return l ? l->impl.state_bytes : 0; }
+
+int b2_lstm_synchronize(b2_lstm *l, b2_stream st) {
+    if (!l) return B2_ERR_BAD_ARG;
+    return l->impl.check_status((cudaStream_t)st);
+}
 
 }  // extern "C"

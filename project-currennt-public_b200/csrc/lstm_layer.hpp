@@ -15,6 +15,11 @@ struct LstmLayerImpl {
     float *ws = nullptr;       // scratch: split-K partials, vector-gradient partials
     size_t ws_floats = 0;
     size_t state_bytes = 0;
+    // persistent kernels: exchange buffers, device status word, running step tag
+    unsigned long long *xchg = nullptr;
+    int *status_dev = nullptr;
+    unsigned tag_next = 1;
+    int check_status(cudaStream_t st);   // synchronises st; returns the kernels' status word
     // optional per-phase timing hooks (set by the layer stack when profiling is on)
     void *prof_ctx = nullptr;
     void (*prof_begin)(void *, const char *) = nullptr;

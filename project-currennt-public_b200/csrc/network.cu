@@ -378,6 +378,10 @@ int NeuralNetwork::updateWeights(float lr, float mom) {
 int NeuralNetwork::synchronize() {
     B2_CUDA(cudaStreamSynchronize(stream));
     B2_CUDA(cudaStreamSynchronize(commStream));
+    for (size_t i = 0; i < layers.size(); ++i) {
+        LstmLayer *l = dynamic_cast<LstmLayer *>(layers[i].get());
+        if (l) B2_TRY(l->impl().check_status(stream));
+    }
     return B2_OK;
 }
 

@@ -114,6 +114,22 @@ def test_config_layer_sizes_reduced_frames(cfg, P, scale, variant):
     parity.compare_run(wl["layers"], got, want, "cfg%d reduced" % cfg, lstm_pad_zero_lens=wl["lens"])
 
 
+@pytest.mark.parametrize("variant", VARIANTS[1:3], ids=VARIANT_IDS[1:3])
+@pytest.mark.parametrize("ls,bi,P,lens", [(2048, 1, 5, [12, 12, 7, 3, 12]), (1024, 0, 1, [9]), (256, 1, 9, [14] * 9),
+                                          (512, 1, 2, [6, 11]), (256, 0, 7, [10, 9, 8, 7, 6, 5, 4])])
+def test_persistent_geometries(ls, bi, P, lens, variant):
+    """Every register-resident geometry of the persistent kernels (128/256/512/1024 units per
+    direction, 1 or 4 sequences per group, sequence counts that do not fill the last group)."""
+    from b2lstm import workloads
+    layers = L(("input", 16), ("blstm" if bi else "lstm", ls), ("feedforward_identity", 8), ("sse", 8))
+    lens = np.array(lens, np.int32)
+    x, tg = workloads.make_fraction(16, 8, P, lens, 31, 32)
+    w = workloads.make_weights(layers, 33, 0.05)
+    want = run_kind(checker(), layers, P, lens, x, tg, w)
+    got = run_gpu(layers, P, lens, x, tg, w, variant)
+    parity.compare_run(layers, got, want, "ls%d bi%d P%d" % (ls, bi, P), lstm_pad_zero_lens=lens)
+
+
 def test_reuse_across_fractions_of_different_length():
     """A net sized for the longest fraction processes shorter and longer fractions back to back
     (stale state in the buffers must not leak into the next fraction)."""
