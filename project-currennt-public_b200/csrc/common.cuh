@@ -55,6 +55,34 @@ enum { PAT_NONE = 0 };
 int gemm_ffma(float *C, long ldc, const float *A, long sam, long sak, const float *B, long sbk, long sbn, int m,
               int n, int k, bool accumulate, float *ws, size_t ws_floats, cudaStream_t st);
 
+// Tensor-core path (gemm_tc.cu): operands are first split into tf32 hi/lo parts, stored densely as
+// [outer][ld] with the contiguous index padded to a multiple of 4 floats.
+struct SplitOperand {
+    const float *hi, *lo;
+    long ld;
+    bool kmajor;   // true: the contraction index k is the contiguous one; false: m (resp. n) is
+};
+// bump arena for the hi/lo copies; grows by reallocation (which waits for the device)
+struct TcScratch {
+    float *base = nullptr;
+    size_t cap = 0, used = 0;
+    int reserve(size_t floats);
+    float *take(size_t floats);
+    void release();
+};
+size_t split_floats(int outer, int inner);
+int split_tf32(const float *src, long s_outer, int outer, int inner, float *hi, float *lo, long ldp, cudaStream_t st);
+int split_operand(TcScratch &sc, const float *src, long s_outer, int outer, int inner, bool kmajor, SplitOperand *out,
+                  cudaStream_t st);
+bool gemm_tc_supported(const SplitOperand &A, const SplitOperand &B, int m, int n, int k);
+int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, int m, int n, int k, bool accumulate,
+            float *ws, size_t ws_floats, int *status, cudaStream_t st);
+bool gemm_wants_tc(long sam, long sak, long sbk, long sbn, int m, int n, int k);
+// picks the tensor-core kernel when the shape qualifies (and sc/status are given), else FFMA
+int gemm_auto(float *C, long ldc, const float *A, long sam, long sak, const float *B, long sbk, long sbn, int m, int n,
+              int k, bool accumulate, bool force_ffma, TcScratch *sc, float *ws, size_t ws_floats, int *status,
+              cudaStream_t st);
+
 // ---- feed-forward / loss / optimizer elementwise kernels (elementwise.cu) -------------------------
 // y[f*ls + u] = act(y + bias*b[u]) over n = frames*ls elements
 int ff_bias_act(float *y, const float *b, float bias, int ls, size_t n, int act, cudaStream_t st);

@@ -1,0 +1,421 @@
+// fp32-accurate GEMM on the 5th-generation tensor cores (tcgen05, sm_100a): 3xTF32 split.
+//
+// Stands where the reference calls helpers::Matrix::assignProduct/addProduct -> cublasSgemm
+// (helpers/Matrix.cu:354-377, helpers/cublas.cu:52-84 of the reference) for the large products of
+// the training path: input projection, error back-projection and the weight-gradient
+// contractions (layers/LstmLayer.cu:1756-1775, 2298-2334 and the per-weight loop :490-572;
+// layers/FeedForwardLayer.cu:1080,1690,1719).
+//
+// Numerics.  Every operand x is split once, by split_tf32(), into hi = rn_tf32(x) and
+// lo = rn_tf32(x - hi); the kernel accumulates a_lo*b_hi + a_hi*b_lo + a_hi*b_hi in fp32 in tensor
+// memory.  The dropped lo*lo term and the rounding of lo are below 2^-21 of |a||b|.
+//
+// Kernel.  One 128 x 128 output tile per block, K in slabs of 32 floats (one 128-byte swizzle
+// row).  Warp 0 (one lane) feeds a 3-stage shared-memory ring with TMA (cp.async.bulk.tensor.2d,
+// SWIZZLE_128B, no multicast), warp 1 (one lane) issues tcgen05.mma.kind::tf32 (M=128, N=128,
+// K=8; 12 per slab) on shared-memory descriptors and releases slots with tcgen05.commit, warps 2-5
+// read the accumulator from TMEM with tcgen05.ld and write C.  Operands may be K-major (k
+// contiguous) or MN-major (m resp. n contiguous); MN-major tiles are fetched as 32-wide column
+// blocks so that they land in the canonical MN-major SWIZZLE_128B layout.  Optional split-K over
+// gridDim.z into scratch (summed by a second kernel in a fixed order).
+//
+// Every mbarrier wait is bounded by a cycle budget; on expiry the block records
+// B2_ERR_STEP_TIMEOUT in *status, leaves its loops, releases its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b2 {
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
+constexpr int TILE_BYTES = BM * BK * 4;                 // 16 KiB: one operand part (hi or lo) of one stage
+constexpr int STAGE_BYTES = 4 * TILE_BYTES;             // A_hi, A_lo, B_hi, B_lo
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024; // + slack to align the ring to 1024 B
+constexpr int NTHREADS = 192;
+constexpr long long WAIT_CYCLES = 4000000000LL;         // about two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait; false when the budget ran out
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try(bar, parity)) return true;
+        if (clock64() - t0 > WAIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"((unsigned long long)map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+// shared-memory matrix descriptor (version 1).  layout type 2 = SWIZZLE_128B (K-major tiles),
+// 1 = SWIZZLE_128B with 32-byte atoms, the only swizzled layout the tensor core accepts for
+// MN-major 32-bit operands
+__device__ __forceinline__ unsigned long long make_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                        unsigned long long layout_type) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr >> 4) & 0x3FFF);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= 1ULL << 46;
+    d |= layout_type << 61;
+    return d;
+}
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, unsigned long long adesc, unsigned long long bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+struct TcArgs {
+    float *C;
+    long ldc;          // column-major C: element (m, n) at n*ldc + m
+    int M, N, K;
+    int kchunk;        // K range handled per gridDim.z slice (multiple of BK)
+    int a_kmajor, b_kmajor;
+    int accumulate;
+    float *ws;         // split-K partials [z][N][M] when gridDim.z > 1
+    int *status;
+};
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
+                   const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo, TcArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int fail_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;   // SWIZZLE_128B atoms need 1024-byte alignment
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
+    const uint32_t accum_bar = bar0 + 8u * (uint32_t)(2 * STAGES);
+
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int kbeg = blockIdx.z * a.kchunk;
+    const int kend = min(a.K, kbeg + a.kchunk);
+    const int nkb = (kend - kbeg + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(accum_bar, 1);
+        fail_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(128)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                if (!mbar_wait(empty_bar(s), ph ^ 1u)) { fail_s = 1; break; }
+                const uint32_t base = ring + (uint32_t)s * STAGE_BYTES;
+                const int k0 = kbeg + kb * BK;
+                mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                if (a.a_kmajor) {
+                    tma_load_2d(base, &mapAhi, k0, m0, full_bar(s));
+                    tma_load_2d(base + TILE_BYTES, &mapAlo, k0, m0, full_bar(s));
+                } else {
+#pragma unroll
+                    for (int b = 0; b < BM / 32; ++b) {
+                        tma_load_2d(base + b * 4096, &mapAhi, m0 + 32 * b, k0, full_bar(s));
+                        tma_load_2d(base + TILE_BYTES + b * 4096, &mapAlo, m0 + 32 * b, k0, full_bar(s));
+                    }
+                }
+                if (a.b_kmajor) {
+                    tma_load_2d(base + 2 * TILE_BYTES, &mapBhi, k0, n0, full_bar(s));
+                    tma_load_2d(base + 3 * TILE_BYTES, &mapBlo, k0, n0, full_bar(s));
+                } else {
+#pragma unroll
+                    for (int b = 0; b < BN / 32; ++b) {
+                        tma_load_2d(base + 2 * TILE_BYTES + b * 4096, &mapBhi, n0 + 32 * b, k0, full_bar(s));
+                        tma_load_2d(base + 3 * TILE_BYTES + b * 4096, &mapBlo, n0 + 32 * b, k0, full_bar(s));
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // instruction descriptor: D=f32, A=B=tf32, M=128, N=128, majors per operand
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((a.a_kmajor ? 0u : 1u) << 15) |
+                                   ((a.b_kmajor ? 0u : 1u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            // K-major: rows of 128 B, 8-row groups 1024 B apart (SBO); one MMA (K=8) advances 32 B inside the row.
+            // MN-major: [k][32 floats] blocks; 32-wide column blocks 4096 B apart (LBO), groups of 4 k-rows
+            // 512 B apart (SBO); one MMA (K=8) advances two such groups = 1024 B.
+            const uint32_t a_lbo = a.a_kmajor ? 16u : 4096u, b_lbo = a.b_kmajor ? 16u : 4096u;
+            const uint32_t a_sbo = a.a_kmajor ? 1024u : 512u, b_sbo = a.b_kmajor ? 1024u : 512u;
+            const unsigned long long a_lt = a.a_kmajor ? 2ULL : 1ULL, b_lt = a.b_kmajor ? 2ULL : 1ULL;
+            const uint32_t a_step = a.a_kmajor ? 32u : 1024u, b_step = a.b_kmajor ? 32u : 1024u;
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                if (!mbar_wait(full_bar(s), ph)) { fail_s = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t base = ring + (uint32_t)s * STAGE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BK / 8; ++kk) {
+                    const unsigned long long ahi = make_desc(base + kk * a_step, a_lbo, a_sbo, a_lt);
+                    const unsigned long long alo = make_desc(base + TILE_BYTES + kk * a_step, a_lbo, a_sbo, a_lt);
+                    const unsigned long long bhi = make_desc(base + 2 * TILE_BYTES + kk * b_step, b_lbo, b_sbo, b_lt);
+                    const unsigned long long blo = make_desc(base + 3 * TILE_BYTES + kk * b_step, b_lbo, b_sbo, b_lt);
+                    mma_tf32(tmem_base, alo, bhi, idesc, (kb | kk) ? 1u : 0u);
+                    mma_tf32(tmem_base, ahi, blo, idesc, 1u);
+                    mma_tf32(tmem_base, ahi, bhi, idesc, 1u);
+                }
+                mma_commit(empty_bar(s));   // slot is free once these MMAs have read it
+            }
+            mma_commit(accum_bar);          // accumulator complete (also arrives when nothing was issued)
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> C ----------------
+        const int q = warp & 3;             // TMEM lane quarter this warp may read
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0));
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (!ok) {
+            if (lane == 0) fail_s = 1;
+        } else if (nkb > 0 || !a.accumulate) {
+            const int m = m0 + 32 * q + lane;
+            const bool split = gridDim.z > 1;
+            float *dst = split ? a.ws + (size_t)blockIdx.z * (size_t)a.M * a.N : a.C;
+            const long ld = split ? (long)a.M : a.ldc;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                if (nkb > 0) {
+                    tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = 0u;
+                }
+                if (m < a.M) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int n = n0 + c0 + j;
+                        if (n < a.N) {
+                            float *p = dst + (size_t)n * ld + m;
+                            float v = __uint_as_float(r[j]);
+                            if (!split && a.accumulate) v += *p;
+                            *p = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (fail_s && threadIdx.x == 0) atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT);
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128) : "memory");
+    }
+}
+
+__global__ void tc_splitk_reduce_kernel(float *__restrict__ C, long ldc, const float *__restrict__ ws, int M, int N,
+                                        int splits, int accumulate) {
+    size_t total = (size_t)M * N;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float s = 0.0f;
+        for (int z = 0; z < splits; ++z) s += ws[(size_t)z * total + i];
+        size_t m = i % M, n = i / M;
+        float *p = C + n * ldc + m;
+        *p = accumulate ? *p + s : s;
+    }
+}
+
+// hi = rn_tf32(x), lo = rn_tf32(x - hi); dense destination [outer][ldp], zero padded to ldp
+__global__ void split_tf32_kernel(const float *__restrict__ src, long s_outer, int outer, int inner, float *__restrict__ hi,
+                                  float *__restrict__ lo, long ldp) {
+    const size_t total = (size_t)outer * ldp;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t o = i / ldp;
+        const int c = (int)(i % ldp);
+        float x = c < inner ? src[o * s_outer + c] : 0.0f;
+        uint32_t h, l;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+        float rem = x - __uint_as_float(h);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rem));
+        hi[i] = __uint_as_float(h);
+        lo[i] = __uint_as_float(l);
+    }
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn g_encode = nullptr;
+
+int get_encode() {
+    if (g_encode) return B2_OK;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    B2_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return B2_ERR_CUDA;
+    }
+    g_encode = (EncodeFn)fn;
+    return B2_OK;
+}
+
+// 2-D fp32 tensor map: dim0 = contiguous extent `inner`, dim1 = `outer` rows `ld` floats apart
+int make_map(CUtensorMap *map, const float *base, long inner, long outer, long ld, int box_inner, int box_outer,
+             bool kmajor) {
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          kmajor ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed (%d) for inner %ld outer %ld ld %ld", (int)r, inner, outer, ld);
+        return B2_ERR_CUDA;
+    }
+    return B2_OK;
+}
+
+bool g_attr_set = false;
+
+}  // namespace
+
+int split_tf32(const float *src, long s_outer, int outer, int inner, float *hi, float *lo, long ldp, cudaStream_t st) {
+    size_t total = (size_t)outer * ldp;
+    if (!total) return B2_OK;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    split_tf32_kernel<<<(int)blocks, 256, 0, st>>>(src, s_outer, outer, inner, hi, lo, ldp);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+bool gemm_tc_supported(const SplitOperand &A, const SplitOperand &B, int m, int n, int k) {
+    if (m < 1 || n < 1 || k < 1) return false;
+    auto ok = [](const SplitOperand &o) {
+        return o.hi && o.lo && (o.ld % 4) == 0 && ((uintptr_t)o.hi % 16) == 0 && ((uintptr_t)o.lo % 16) == 0;
+    };
+    return ok(A) && ok(B);
+}
+
+// C(m x n) (+)= A' B' from pre-split operands.  K-major A: rows m, `ld` floats apart, k contiguous;
+// MN-major A: rows k, m contiguous.  Likewise B with n.
+int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, int m, int n, int k, bool accumulate, float *ws,
+            size_t ws_floats, int *status, cudaStream_t st) {
+    B2_TRY(get_encode());
+    if (!g_attr_set) {
+        B2_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        g_attr_set = true;
+    }
+    CUtensorMap mAh, mAl, mBh, mBl;
+    if (A.kmajor) {
+        B2_TRY(make_map(&mAh, A.hi, k, m, A.ld, BK, BM, true));
+        B2_TRY(make_map(&mAl, A.lo, k, m, A.ld, BK, BM, true));
+    } else {
+        B2_TRY(make_map(&mAh, A.hi, m, k, A.ld, 32, BK, false));
+        B2_TRY(make_map(&mAl, A.lo, m, k, A.ld, 32, BK, false));
+    }
+    if (B.kmajor) {
+        B2_TRY(make_map(&mBh, B.hi, k, n, B.ld, BK, BN, true));
+        B2_TRY(make_map(&mBl, B.lo, k, n, B.ld, BK, BN, true));
+    } else {
+        B2_TRY(make_map(&mBh, B.hi, n, k, B.ld, 32, BK, false));
+        B2_TRY(make_map(&mBl, B.lo, n, k, B.ld, 32, BK, false));
+    }
+    dim3 grid((m + BM - 1) / BM, (n + BN - 1) / BN, 1);
+    const int tiles = grid.x * grid.y;
+    // Split K (a) to fill the 148 SMs when there are few output tiles and (b) to bound the length of
+    // one tensor-memory accumulation chain; the partial sums are added with fp32 FADD in a fixed order.
+    int splits = 1;
+    if (ws) {
+        if (tiles < 148 && k >= 1024) splits = (148 + tiles - 1) / tiles;
+        const int by_len = (k + 8191) / 8192;
+        if (by_len > splits) splits = by_len;
+        const int maxs = (k + 255) / 256;
+        if (splits > maxs) splits = maxs;
+        const size_t per = (size_t)m * n;
+        if ((size_t)splits * per > ws_floats) splits = (int)(ws_floats / per);
+        if (splits < 1) splits = 1;
+    }
+    int kchunk = (k + splits - 1) / splits;
+    kchunk = (kchunk + BK - 1) / BK * BK;
+    splits = (k + kchunk - 1) / kchunk;
+    grid.z = splits;
+    TcArgs a;
+    a.C = C; a.ldc = ldc; a.M = m; a.N = n; a.K = k; a.kchunk = kchunk;
+    a.a_kmajor = A.kmajor ? 1 : 0; a.b_kmajor = B.kmajor ? 1 : 0;
+    a.accumulate = accumulate ? 1 : 0; a.ws = ws; a.status = status;
+    gemm_tf32x3_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(mAh, mAl, mBh, mBl, a);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
+    if (splits > 1) {
+        size_t total = (size_t)m * n;
+        int blocks = (int)((total + 255) / 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        tc_splitk_reduce_kernel<<<blocks, 256, 0, st>>>(C, ldc, ws, m, n, splits, accumulate ? 1 : 0);
+        count_launch();
+        B2_CUDA(cudaGetLastError());
+    }
+    return B2_OK;
+}
+
+}  // namespace b2

@@ -46,6 +46,7 @@ int LstmLayerImpl::create(const b2_lstm_desc &d) {
     size_t vg = ((frames + 255) / 256) * 7 * ls;
     ws_floats = vg > ((size_t)6 << 20) ? vg : ((size_t)6 << 20);
     B2_CUDA(cudaMalloc(&ws, ws_floats * sizeof(float)));
+    if (!scratch) { own_scratch = new TcScratch; scratch = own_scratch; }
     B2_CUDA(cudaMalloc(&status_dev, sizeof(int)));
     B2_CUDA(cudaMemset(status_dev, 0, sizeof(int)));
     size_t xw = lstm_persistent_xchg_words(els, d.parallel_sequences);
@@ -65,6 +66,7 @@ int LstmLayerImpl::create(const b2_lstm_desc &d) {
 void LstmLayerImpl::destroy() {
     cudaFree(bufs.acts); cudaFree(bufs.cells); cudaFree(bufs.deltas); cudaFree(bufs.cerr); cudaFree(bufs.wrecT);
     cudaFree(ws); cudaFree(xchg); cudaFree(status_dev);
+    if (own_scratch) { own_scratch->release(); delete own_scratch; own_scratch = nullptr; scratch = nullptr; }
     bufs = LstmBuffers();
     ws = nullptr; xchg = nullptr; status_dev = nullptr;
 }
@@ -121,29 +123,66 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
         if (rc == 1) rc = lstm_backward_stepwise(s, bufs, w, dy, st);
         B2_TRY(rc);
     }
+    const int K = N - P;
+    const bool tc = !force_ffma && scratch && gemm_wants_tc(1, pls, 4 * ls, 1, pls, 4 * ls, N);
+    SplitOperand sD{}, sX{}, sY{}, sW{};
+    if (tc) {
+        // every operand of the four contractions is split into tf32 hi/lo parts ONCE and reused:
+        // deltas feed dX, dW_in and dW_rec; the layouts [frame][unit] serve both as K-major and
+        // as MN-major operands, only the role of the contiguous index changes
+        Phase ph(*this, "lstm_split_tf32");
+        B2_TRY(scratch->reserve(split_floats(N, 4 * ls) + split_floats(N, pls) + split_floats(N, ls) +
+                                split_floats(4 * ls, pls)));
+        scratch->used = 0;
+        B2_TRY(split_operand(*scratch, bufs.deltas, 4 * ls, N, 4 * ls, true, &sD, st));
+        B2_TRY(split_operand(*scratch, x, pls, N, pls, false, &sX, st));
+        B2_TRY(split_operand(*scratch, y, ls, N, ls, false, &sY, st));
+        B2_TRY(split_operand(*scratch, w, pls, 4 * ls, pls, false, &sW, st));
+    }
     // error to the preceding layer (reference: 4*D Sgemm, LstmLayer.cu:2298-2334): dX = W_in * deltas
     if (dx) {
         Phase ph(*this, "lstm_dx_gemm");
-        B2_TRY(gemm(dx, pls, w, 1, pls, bufs.deltas, 1, 4 * ls, pls, N, 4 * ls, false, st));
+        if (tc) {
+            SplitOperand A = sW, B = sD;
+            A.kmajor = false; B.kmajor = true;
+            B2_TRY(gemm_tc(dx, pls, A, B, pls, N, 4 * ls, false, ws, ws_floats, status_dev, st));
+        } else {
+            B2_TRY(gemm(dx, pls, w, 1, pls, bufs.deltas, 1, 4 * ls, pls, N, 4 * ls, false, st));
+        }
     }
     // input weight gradients (reference: one thread per weight, serial over frames,
     // LstmLayer.cu:490-522): dW_in(pls x 4ls) = X * deltas^T, written straight into the weight layout
     {
         Phase ph(*this, "lstm_dw_in_gemm");
-        B2_TRY(gemm(dw, pls, x, 1, pls, bufs.deltas, 4 * ls, 1, pls, 4 * ls, N, false, st));
+        if (tc) {
+            SplitOperand A = sX, B = sD;
+            A.kmajor = false; B.kmajor = false;
+            B2_TRY(gemm_tc(dw, pls, A, B, pls, 4 * ls, N, false, ws, ws_floats, status_dev, st));
+        } else {
+            B2_TRY(gemm(dw, pls, x, 1, pls, bufs.deltas, 4 * ls, 1, pls, 4 * ls, N, false, st));
+        }
     }
     // recurrent weight gradients (LstmLayer.cu:543-572,629-636): for gate g, direction d
     //   dW_rec[g][d](k, j) = sum_f h_d[k; f -/+ P] * delta_g,d[j; f], skipping the first (last) timestep
-    const int K = N - P;
     {
-    Phase ph(*this, "lstm_dw_rec_gemm");
-    for (int d = 0; d < D; ++d)
-        for (int g = 0; g < 4; ++g) {
-            float *C = dw + off.rec + ((size_t)g * ls + (size_t)d * els) * els;
-            const float *A = y + (size_t)d * els + (d ? (size_t)P * ls : 0);
-            const float *B = bufs.deltas + (size_t)g * ls + (size_t)d * els + (d ? 0 : (size_t)P * 4 * ls);
-            B2_TRY(gemm(C, els, A, 1, ls, B, 4 * ls, 1, els, els, K, false, st));
-        }
+        Phase ph(*this, "lstm_dw_rec_gemm");
+        const bool tc_rec = tc && (els % 4) == 0 && gemm_wants_tc(1, ls, 4 * ls, 1, els, els, K);
+        for (int d = 0; d < D; ++d)
+            for (int g = 0; g < 4; ++g) {
+                float *C = dw + off.rec + ((size_t)g * ls + (size_t)d * els) * els;
+                if (tc_rec) {
+                    SplitOperand A = sY, B = sD;
+                    const size_t ao = (size_t)d * els + (d ? (size_t)P * sY.ld : 0);
+                    const size_t bo = (size_t)g * ls + (size_t)d * els + (d ? 0 : (size_t)P * sD.ld);
+                    A.hi += ao; A.lo += ao; A.kmajor = false;
+                    B.hi += bo; B.lo += bo; B.kmajor = false;
+                    B2_TRY(gemm_tc(C, els, A, B, els, els, K, false, ws, ws_floats, status_dev, st));
+                } else {
+                    const float *A = y + (size_t)d * els + (d ? (size_t)P * ls : 0);
+                    const float *B = bufs.deltas + (size_t)g * ls + (size_t)d * els + (d ? 0 : (size_t)P * 4 * ls);
+                    B2_TRY(gemm_ffma(C, els, A, 1, ls, B, 4 * ls, 1, els, els, K, false, ws, ws_floats, st));
+                }
+            }
     }
     Phase ph(*this, "lstm_vector_grads");
     B2_TRY(lstm_vector_grads(s, bufs, dw, ws, ws_floats, st));
@@ -156,7 +195,7 @@ int LstmLayerImpl::check_status(cudaStream_t st) {
     B2_CUDA(cudaStreamSynchronize(st));
     if (v != 0) {
         B2_CUDA(cudaMemsetAsync(status_dev, 0, sizeof(int), st));
-        set_error("a persistent recurrence kernel gave up waiting for a peer block (status %d)", v);
+        set_error("a kernel of this layer gave up a bounded wait (status %d)", v);
         return v;
     }
     return B2_OK;
@@ -164,7 +203,7 @@ int LstmLayerImpl::check_status(cudaStream_t st) {
 
 int LstmLayerImpl::gemm(float *C, long ldc, const float *A, long sam, long sak, const float *B, long sbk, long sbn,
                         int m, int n, int k, bool acc, cudaStream_t st) {
-    return gemm_ffma(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, acc, ws, ws_floats, st);
+    return gemm_auto(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, acc, force_ffma, scratch, ws, ws_floats, status_dev, st);
 }
 
 }  // namespace b2

@@ -15,6 +15,9 @@ struct LstmLayerImpl {
     float *ws = nullptr;       // scratch: split-K partials, vector-gradient partials
     size_t ws_floats = 0;
     size_t state_bytes = 0;
+    // arena for the tf32 hi/lo operand copies of the tensor-core GEMMs: the layer stack lends its
+    // shared one (set before create()); a stand-alone layer makes its own
+    TcScratch *scratch = nullptr, *own_scratch = nullptr;
     // persistent kernels: exchange buffers, device status word, running step tag
     unsigned long long *xchg = nullptr;
     int *status_dev = nullptr;

@@ -139,6 +139,7 @@ int LstmLayer::init() {
     b2_lstm_desc d;
     d.parallel_sequences = P_; d.max_seq_length = maxT_; d.prev_size = prev_->size(); d.size = size_;
     d.bidirectional = bidirectional_ ? 1 : 0; d.bias = bias_;
+    impl_.scratch = &net_.tcScratch;
     B2_TRY(impl_.create(d));
     impl_.prof_ctx = &net_;
     impl_.prof_begin = prof_begin_cb;
@@ -195,7 +196,8 @@ int SsePostOutputLayer::computeBackwardPass(int) {
 NeuralNetwork::~NeuralNetwork() {
     if (dp) dp_detach(*this);
     layers.clear();
-    cudaFree(ws); cudaFree(inDev); cudaFree(tgDev); cudaFree(patDev);
+    cudaFree(ws); cudaFree(inDev); cudaFree(tgDev); cudaFree(patDev); cudaFree(statusDev);
+    tcScratch.release();
     for (size_t i = 0; i < eventPool.size(); ++i) cudaEventDestroy(eventPool[i]);
     for (size_t i = 0; i < prof.size(); ++i) { cudaEventDestroy(prof[i].a); cudaEventDestroy(prof[i].b); }
     for (size_t i = 0; i < gradReady.size(); ++i) cudaEventDestroy(gradReady[i]);
@@ -205,7 +207,7 @@ NeuralNetwork::~NeuralNetwork() {
 
 int NeuralNetwork::gemm(float *C, long ldc, const float *A, long sam, long sak, const float *B, long sbk, long sbn,
                         int m, int n, int k, bool acc) {
-    return gemm_ffma(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, acc, ws, wsFloats, stream);
+    return gemm_auto(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, acc, forceFfma, &tcScratch, ws, wsFloats, statusDev, stream);
 }
 
 int NeuralNetwork::create(const char *networkJson, int P_, int maxT_, unsigned seed) {
@@ -235,6 +237,8 @@ int NeuralNetwork::create(const char *networkJson, int P_, int maxT_, unsigned s
         B2_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
         B2_CUDA(cudaStreamCreateWithPriority(&stream, cudaStreamNonBlocking, lo));
         B2_CUDA(cudaStreamCreateWithPriority(&commStream, cudaStreamNonBlocking, hi));
+        B2_CUDA(cudaMalloc(&statusDev, sizeof(int)));
+        B2_CUDA(cudaMemset(statusDev, 0, sizeof(int)));
         for (size_t i = 0; i < L.arr.size(); ++i) {
             const json::Value &j = L.arr[i];
             const std::string ty = j.at("type").str;
@@ -382,6 +386,13 @@ int NeuralNetwork::synchronize() {
         LstmLayer *l = dynamic_cast<LstmLayer *>(layers[i].get());
         if (l) B2_TRY(l->impl().check_status(stream));
     }
+    int v = 0;
+    B2_CUDA(cudaMemcpy(&v, statusDev, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v != 0) {
+        B2_CUDA(cudaMemset(statusDev, 0, sizeof(int)));
+        set_error("a tensor-core GEMM gave up a bounded wait (status %d)", v);
+        return v;
+    }
     return B2_OK;
 }
 
@@ -427,8 +438,30 @@ int b2_matrix_multiply(float *C, int ldc, const float *A, int lda, int transA, c
     if (transA && transB) { set_error("b2_matrix_multiply: transposing both operands is not supported"); return B2_ERR_BAD_ARG; }
     long sam = transA ? lda : 1, sak = transA ? 1 : lda;
     long sbk = transB ? ldb : 1, sbn = transB ? 1 : ldb;
-    (void)force_ffma;
-    return gemm_ffma(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, accumulate != 0, nullptr, 0, (cudaStream_t)stream);
+    // stand-alone calls share one operand arena, split-K scratch and status word per process
+    static TcScratch sc;
+    static int *status = nullptr;
+    static float *ws = nullptr;
+    static const size_t wsFloats = (size_t)8 << 20;
+    if (!status) {
+        B2_CUDA(cudaMalloc(&status, sizeof(int)));
+        B2_CUDA(cudaMemset(status, 0, sizeof(int)));
+        B2_CUDA(cudaMalloc(&ws, wsFloats * sizeof(float)));
+    }
+    B2_TRY(gemm_auto(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, accumulate != 0, force_ffma != 0, &sc, ws, wsFloats, status,
+                     (cudaStream_t)stream));
+    if (!force_ffma && gemm_wants_tc(sam, sak, sbk, sbn, m, n, k)) {
+        // the arena may be reused by the next call: finish, and report a timed-out wait
+        int v = 0;
+        B2_CUDA(cudaMemcpyAsync(&v, status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+        B2_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+        if (v != 0) {
+            B2_CUDA(cudaMemset(status, 0, sizeof(int)));
+            set_error("b2_matrix_multiply: the tensor-core kernel gave up a bounded wait (status %d)", v);
+            return v;
+        }
+    }
+    return B2_OK;
 }
 
 int b2_net_create(const char *network_json, int P, int maxT, unsigned seed, b2_net **out) {

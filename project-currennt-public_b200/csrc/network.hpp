@@ -154,6 +154,9 @@ public:
     // shared scratch for GEMM split-K and column sums
     float *ws = nullptr;
     size_t wsFloats = 0;
+    // tensor-core GEMMs: arena for the tf32 hi/lo operand copies, device status word of their waits
+    TcScratch tcScratch;
+    int *statusDev = nullptr;
     // device copies of the current fraction
     float *inDev = nullptr, *tgDev = nullptr;
     char *patDev = nullptr;

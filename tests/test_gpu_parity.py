@@ -220,6 +220,30 @@ def test_matrix_multiply_wrapper():
                 assert np.abs(tC.cpu().numpy().T - 2 * want).max() <= 4e-6 * scale * 8
 
 
+def test_tensor_core_gemm_keeps_fp32_accuracy_on_long_contractions():
+    """The weight-gradient products contract over all frames of a fraction (tens of thousands of
+    terms).  The 3xTF32 tensor-core kernel must stay as close to the float64 result as a plain fp32
+    FFMA kernel does: relative L2 error below 2e-6 and within a small factor of the FFMA error."""
+    import torch
+    import b2lstm
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(11)
+    for (m, n, k) in [(256, 384, 40000), (512, 2048, 9000)]:
+        A = (rng.standard_normal((k, m)) * 0.5).astype(np.float32)        # m x k column-major
+        B = (rng.standard_normal((k, n)) * 0.1).astype(np.float32)        # B^T stored n x k col-major -> transB
+        want = A.T.astype(np.float64) @ B.astype(np.float64)
+        tA, tB = torch.from_numpy(A).to(dev), torch.from_numpy(B).to(dev)
+        errs = {}
+        for ffma in (1, 0):
+            tC = torch.zeros((n, m), device=dev)
+            b2lstm.matrix_multiply(tC, m, tA, m, 0, tB, n, 1, m, n, k, accumulate=False, force_ffma=ffma)
+            torch.cuda.synchronize()
+            got = tC.cpu().numpy().T.astype(np.float64)
+            errs[ffma] = np.linalg.norm(got - want) / np.linalg.norm(want)
+        print("gemm %dx%dx%d rel L2 error: ffma %.3g tensor %.3g" % (m, n, k, errs[1], errs[0]))
+        assert errs[0] < 2e-6 and errs[0] < 8 * errs[1] + 2e-7, errs
+
+
 def test_errors_are_status_codes():
     import b2lstm
     layers = L(("input", 4), ("lstm", 4), ("sse", 4))
