@@ -14,7 +14,8 @@
 // row).  Warp 0 (one lane) feeds a 3-stage shared-memory ring with TMA (cp.async.bulk.tensor.2d,
 // SWIZZLE_128B, no multicast), warp 1 (one lane) issues tcgen05.mma.kind::tf32 (M=128, N=128,
 // K=8; 12 per slab) on shared-memory descriptors and releases slots with tcgen05.commit, warps 2-5
-// read the accumulator from TMEM with tcgen05.ld and write C.  Operands may be K-major (k
+// drain the double-buffered main accumulator from TMEM with tcgen05.ld every SEG slabs, add the
+// segments in registers and finally write C.  Operands may be K-major (k
 // contiguous) or MN-major (m resp. n contiguous); MN-major tiles are fetched as 32-wide column
 // blocks so that they land in the canonical MN-major SWIZZLE_128B layout.  Optional split-K over
 // gridDim.z into scratch (summed by a second kernel in a fixed order).
@@ -33,6 +34,8 @@ constexpr int TILE_BYTES = BM * BK * 4;                 // 16 KiB: one operand p
 constexpr int STAGE_BYTES = 4 * TILE_BYTES;             // A_hi, A_lo, B_hi, B_lo
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024; // + slack to align the ring to 1024 B
 constexpr int NTHREADS = 192;
+constexpr int SEG = 2;                                  // slabs per drained accumulator segment
+constexpr int TMEM_COLS = 512;                          // 2 x 128 main accumulator + 128 cross terms (power of two)
 constexpr long long WAIT_CYCLES = 4000000000LL;         // about two seconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -124,7 +127,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
                    const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo, TcArgs a) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 4];
     __shared__ uint32_t tmem_base_s;
     __shared__ int fail_s;
 
@@ -133,7 +136,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * (uint32_t)s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
-    const uint32_t accum_bar = bar0 + 8u * (uint32_t)(2 * STAGES);
+    // the main (hi*hi) accumulator is double-buffered in tensor memory and drained every SEG slabs
+    auto big_full = [&](int b) { return bar0 + 8u * (uint32_t)(2 * STAGES + b); };
+    auto big_empty = [&](int b) { return bar0 + 8u * (uint32_t)(2 * STAGES + 2 + b); };
 
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const int kbeg = blockIdx.z * a.kchunk;
@@ -142,13 +147,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(big_full(b), 1); mbar_init(big_empty(b), 4); }
         fail_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(128)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -202,56 +207,86 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
             const uint32_t a_sbo = a.a_kmajor ? 1024u : 512u, b_sbo = a.b_kmajor ? 1024u : 512u;
             const unsigned long long a_lt = a.a_kmajor ? 2ULL : 1ULL, b_lt = a.b_kmajor ? 2ULL : 1ULL;
             const uint32_t a_step = a.a_kmajor ? 32u : 1024u, b_step = a.b_kmajor ? 32u : 1024u;
+            // Tensor-memory accumulation rounds toward zero, so a long chain drifts linearly with its
+            // length.  Two measures keep fp32 accuracy: the cross terms (2^-11 of the main term) get an
+            // accumulator of their own, and the main accumulator is handed to the epilogue warps every
+            // SEG slabs (SEG*4 MMAs), which add the segments in registers with round-to-nearest.
+            const uint32_t t_small = tmem_base + 2 * BN;
             bool ok = true;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-                if (!mbar_wait(full_bar(s), ph)) { fail_s = 1; ok = false; break; }
+            const int nseg = (nkb + SEG - 1) / SEG;
+            for (int seg = 0; seg < nseg && ok; ++seg) {
+                const int buf = seg & 1;
+                const uint32_t use = (uint32_t)(seg >> 1);
+                if (!mbar_wait(big_empty(buf), (use & 1u) ^ 1u)) { fail_s = 1; ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t base = ring + (uint32_t)s * STAGE_BYTES;
+                const uint32_t t_big = tmem_base + (uint32_t)buf * BN;
+                const int kb_end = min(nkb, (seg + 1) * SEG);
+                for (int kb = seg * SEG; kb < kb_end; ++kb) {
+                    const int s = kb % STAGES;
+                    const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                    if (!mbar_wait(full_bar(s), ph)) { fail_s = 1; ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t base = ring + (uint32_t)s * STAGE_BYTES;
 #pragma unroll
-                for (int kk = 0; kk < BK / 8; ++kk) {
-                    const unsigned long long ahi = make_desc(base + kk * a_step, a_lbo, a_sbo, a_lt);
-                    const unsigned long long alo = make_desc(base + TILE_BYTES + kk * a_step, a_lbo, a_sbo, a_lt);
-                    const unsigned long long bhi = make_desc(base + 2 * TILE_BYTES + kk * b_step, b_lbo, b_sbo, b_lt);
-                    const unsigned long long blo = make_desc(base + 3 * TILE_BYTES + kk * b_step, b_lbo, b_sbo, b_lt);
-                    mma_tf32(tmem_base, alo, bhi, idesc, (kb | kk) ? 1u : 0u);
-                    mma_tf32(tmem_base, ahi, blo, idesc, 1u);
-                    mma_tf32(tmem_base, ahi, bhi, idesc, 1u);
+                    for (int kk = 0; kk < BK / 8; ++kk) {
+                        const unsigned long long ahi = make_desc(base + kk * a_step, a_lbo, a_sbo, a_lt);
+                        const unsigned long long alo = make_desc(base + TILE_BYTES + kk * a_step, a_lbo, a_sbo, a_lt);
+                        const unsigned long long bhi = make_desc(base + 2 * TILE_BYTES + kk * b_step, b_lbo, b_sbo, b_lt);
+                        const unsigned long long blo = make_desc(base + 3 * TILE_BYTES + kk * b_step, b_lbo, b_sbo, b_lt);
+                        mma_tf32(t_small, alo, bhi, idesc, (kb | kk) ? 1u : 0u);
+                        mma_tf32(t_small, ahi, blo, idesc, 1u);
+                        mma_tf32(t_big, ahi, bhi, idesc, (kb != seg * SEG || kk) ? 1u : 0u);
+                    }
+                    mma_commit(empty_bar(s));   // slot is free once these MMAs have read it
                 }
-                mma_commit(empty_bar(s));   // slot is free once these MMAs have read it
+                mma_commit(big_full(buf));      // everything issued so far (cross terms included) is complete
             }
-            mma_commit(accum_bar);          // accumulator complete (also arrives when nothing was issued)
         }
     } else {
-        // ---------------- epilogue: TMEM -> registers -> C ----------------
+        // ---------------- epilogue: drain segments from TMEM, sum in registers, write C ----------------
         const int q = warp & 3;             // TMEM lane quarter this warp may read
-        const bool ok = __all_sync(0xffffffffu, mbar_wait(accum_bar, 0));
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
+        float acc[BN];
+#pragma unroll
+        for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
+        const int nseg = (nkb + SEG - 1) / SEG;
+        bool ok = true;
+        for (int seg = 0; seg < nseg; ++seg) {
+            const int buf = seg & 1;
+            const uint32_t use = (uint32_t)(seg >> 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(big_full(buf), use & 1u));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(lane_base + (uint32_t)(buf * BN + c0), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(big_empty(buf)) : "memory");
+        }
         if (!ok) {
             if (lane == 0) fail_s = 1;
-        } else if (nkb > 0 || !a.accumulate) {
+        } else {
             const int m = m0 + 32 * q + lane;
             const bool split = gridDim.z > 1;
             float *dst = split ? a.ws + (size_t)blockIdx.z * (size_t)a.M * a.N : a.C;
             const long ld = split ? (long)a.M : a.ldc;
-#pragma unroll 1
+#pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
-                if (nkb > 0) {
-                    tmem_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)c0, r);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = 0u;
-                }
+                tmem_ld32(lane_base + (uint32_t)(2 * BN + c0), r);     // the cross-term accumulator
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (m < a.M) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int n = n0 + c0 + j;
                         if (n < a.N) {
                             float *p = dst + (size_t)n * ld + m;
-                            float v = __uint_as_float(r[j]);
+                            float v = acc[c0 + j] + __uint_as_float(r[j]);
                             if (!split && a.accumulate) v += *p;
                             *p = v;
                         }
@@ -264,7 +299,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
     __syncthreads();
     if (fail_s && threadIdx.x == 0) atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT);
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -383,13 +418,11 @@ int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, in
     }
     dim3 grid((m + BM - 1) / BM, (n + BN - 1) / BN, 1);
     const int tiles = grid.x * grid.y;
-    // Split K (a) to fill the 148 SMs when there are few output tiles and (b) to bound the length of
-    // one tensor-memory accumulation chain; the partial sums are added with fp32 FADD in a fixed order.
+    // Split K to fill the 148 SMs when there are few output tiles; the partial sums are added with
+    // fp32 FADD in a fixed order.
     int splits = 1;
     if (ws) {
         if (tiles < 148 && k >= 1024) splits = (148 + tiles - 1) / tiles;
-        const int by_len = (k + 8191) / 8192;
-        if (by_len > splits) splits = by_len;
         const int maxs = (k + 255) / 256;
         if (splits > maxs) splits = maxs;
         const size_t per = (size_t)m * n;
