@@ -59,6 +59,18 @@ const char *b2_version(void);
 int b2_matrix_multiply(float *C, int ldc, const float *A, int lda, int transA, const float *B, int ldb,
                        int transB, int m, int n, int k, int accumulate, int force_ffma, b2_stream stream);
 
+/* The same product for hosts that must not have device memory allocated on their behalf (all of
+ * HBM already owned by the host program's pool, or no tolerance for cudaMalloc's device-wide
+ * synchronisation).  No counterpart in the reference toolkit.  Always the FFMA kernel; its split-K
+ * partial sums live in a fixed 16 MiB array inside the library image (held by every GPU that loads
+ * the library, until exit) instead of an allocation, so the call allocates nothing.
+ * Limit: m*n <= 2^21 output elements, otherwise B2_ERR_BAD_SHAPE.
+ * The first call on a device looks up the array's device address; make it outside any stream
+ * capture.  All calls on a device share the array: calls whose kernels can overlap on the GPU
+ * (different streams) race on it and must be serialised by the caller. */
+int b2_matrix_multiply_noalloc(float *C, int ldc, const float *A, int lda, int transA, const float *B, int ldb,
+                               int transB, int m, int n, int k, int accumulate, b2_stream stream);
+
 /* ------------------------------------------------------------------------------------------
  * layers::LstmLayer<Gpu>                                    (layers/LstmLayer.hpp:168-308)
  * ------------------------------------------------------------------------------------------ */

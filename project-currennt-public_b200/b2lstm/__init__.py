@@ -3,9 +3,9 @@ LSTM / BLSTM training path.  The library is the product; this package only loads
 generates the synthetic workloads and launches processes.  There is no CPU fallback: importing
 works without a GPU (symbols can be inspected), every compute call needs one.
 """
-from .lib import (B2Error, LstmLayer, Net, lib, library_path, lstm_num_weights, matrix_multiply,
+from .lib import (B2Error, LstmLayer, Net, lib, library_path, lstm_num_weights, matrix_multiply, matrix_multiply_noalloc,
                   dp_unique_id)
 from . import workloads
 
-__all__ = ["B2Error", "LstmLayer", "Net", "lib", "library_path", "lstm_num_weights", "matrix_multiply",
+__all__ = ["B2Error", "LstmLayer", "Net", "lib", "library_path", "lstm_num_weights", "matrix_multiply", "matrix_multiply_noalloc",
            "dp_unique_id", "workloads"]

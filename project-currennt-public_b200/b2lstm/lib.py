@@ -31,6 +31,8 @@ SIGNATURES = {
     "b2_version": (C.c_char_p, []),
     "b2_matrix_multiply": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int,
                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "b2_matrix_multiply_noalloc": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
+                                             C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "b2_lstm_num_weights": (C.c_size_t, [C.c_void_p]),
     "b2_lstm_create": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "b2_lstm_destroy": (None, [C.c_void_p]),
@@ -122,6 +124,13 @@ def lstm_num_weights(prev_size, size, bidirectional):
 def matrix_multiply(Cm, ldc, A, lda, transA, B, ldb, transB, m, n, k, accumulate=False, force_ffma=False, stream=None):
     _check(lib().b2_matrix_multiply(_dev(Cm), ldc, _dev(A), lda, int(transA), _dev(B), ldb, int(transB), m, n, k,
                                     int(accumulate), int(force_ffma), stream))
+
+
+def matrix_multiply_noalloc(Cm, ldc, A, lda, transA, B, ldb, transB, m, n, k, accumulate=False, stream=None):
+    """b2_matrix_multiply_noalloc: the FFMA product with its scratch in a fixed array of the library
+    image, for hosts that cannot have device memory allocated for them (see include/b2lstm.h)."""
+    _check(lib().b2_matrix_multiply_noalloc(_dev(Cm), ldc, _dev(A), lda, int(transA), _dev(B), ldb, int(transB), m, n, k,
+                                            int(accumulate), stream))
 
 
 class LstmLayer:

@@ -171,3 +171,56 @@ int gemm_ffma(float *C, long ldc, const float *A, long sam, long sak, const floa
 }
 
 }  // namespace b2
+
+// ---- b2_matrix_multiply_noalloc ------------------------------------------------------------------
+// The split-K scratch of the FFMA GEMM normally comes from cudaMalloc.  Some hosts cannot let a
+// library do that: a training program that has handed all of HBM to its own pool (a caching
+// allocator, or Thrust vectors sized to fill the card), where a further cudaMalloc fails or
+// fragments; or a latency-sensitive loop in which cudaMalloc's device-wide synchronisation would
+// stall work on other streams.  For them this entry point keeps the scratch in a fixed array that
+// is part of the library image: every GPU that loads the library holds NOALLOC_SCRATCH_FLOATS * 4
+// bytes (16 MiB) until the process exits.
+//
+// The array name is only a host-side handle; the kernel needs its device address, which differs per
+// GPU.  It is looked up with cudaGetSymbolAddress the first time the entry point runs on a device
+// (with that device current) and cached.  Make that first call outside any stream capture.
+// All calls on a device share the array and find the previous call's partial sums in it: nothing in
+// it has to start at zero, because a launch writes every partial it later reads, but two calls whose
+// kernels overlap on the GPU (different streams) race on it -- serialise them.
+namespace {
+constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)1 << 22;
+constexpr size_t NOALLOC_MAX_MN = (size_t)1 << 21;   // largest m*n accepted: leaves room for a 2-way split
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+float *g_noalloc_ptr[NOALLOC_MAX_DEVICES];           // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int b2_matrix_multiply_noalloc(float *C, int ldc, const float *A, int lda, int transA, const float *B, int ldb,
+                                          int transB, int m, int n, int k, int accumulate, b2_stream stream) {
+    using namespace b2;
+    if (!C || !A || !B) { set_error("b2_matrix_multiply_noalloc: null pointer"); return B2_ERR_BAD_ARG; }
+    if (transA && transB) {
+        set_error("b2_matrix_multiply_noalloc: transposing both operands is not supported");
+        return B2_ERR_BAD_ARG;
+    }
+    if (m < 0 || n < 0 || k < 0 || (size_t)m * (size_t)n > NOALLOC_MAX_MN) {
+        set_error("b2_matrix_multiply_noalloc: m*n = %zu exceeds the fixed scratch limit of %zu output elements",
+                  (size_t)m * (size_t)n, NOALLOC_MAX_MN);
+        return B2_ERR_BAD_SHAPE;
+    }
+    int dev = -1;
+    B2_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+        set_error("b2_matrix_multiply_noalloc: device ordinal %d outside 0..%d", dev, NOALLOC_MAX_DEVICES - 1);
+        return B2_ERR_BAD_ARG;
+    }
+    if (!g_noalloc_ptr[dev]) {
+        float *p = nullptr;
+        B2_CUDA(cudaGetSymbolAddress((void **)&p, g_noalloc_scratch));
+        g_noalloc_ptr[dev] = p;
+    }
+    const long sam = transA ? lda : 1, sak = transA ? 1 : lda;
+    const long sbk = transB ? ldb : 1, sbn = transB ? 1 : ldb;
+    return gemm_ffma(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, accumulate != 0, g_noalloc_ptr[dev], NOALLOC_SCRATCH_FLOATS,
+                     (cudaStream_t)stream);
+}
