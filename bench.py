@@ -203,7 +203,8 @@ def main():
     c = workloads.CONFIGS[cfg]
     if args.strong and world > 1:
         full = workloads.build(cfg)
-        idx = np.arange(rank, c["P"], world)       # deal the length-sorted sequences round-robin
+        from b2lstm import dp
+        idx = dp.shard_indices(c["P"], rank, world)   # deal the length-sorted sequences in snake order
         wl = dict(full, P=len(idx), lens=full["lens"][idx], x=np.ascontiguousarray(full["x"][:, idx]),
                   tg=np.ascontiguousarray(full["tg"][:, idx]))
         T = int(wl["lens"].max())
