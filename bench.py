@@ -176,9 +176,12 @@ def main():
     ap.add_argument("--ffma", type=int, default=0)
     ap.add_argument("--cpu-seconds", type=float, default=20.0, help="budget of the CPU baseline sample")
     ap.add_argument("--cpu-scale", type=float, default=0.02)
+    ap.add_argument("--frames-scale", type=float, default=1.0,
+                    help="shorten every sequence by this factor (profiler captures only; such a line is not a bench value)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "b2lstm" else max(args.warmup, 1)
+    if args.frames_scale == 1.0:
+        args.warmup = max(args.warmup, 3) if args.impl == "b2lstm" else max(args.warmup, 1)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -210,7 +213,7 @@ def main():
         T = int(wl["lens"].max())
         wl["x"], wl["tg"] = wl["x"][:T], wl["tg"][:T]
     else:
-        wl = workloads.build(cfg, rank=rank)
+        wl = workloads.build(cfg, rank=rank, scale_frames=args.frames_scale)
     layers, P, lens = wl["layers"], wl["P"], wl["lens"]
     T = int(lens.max())
     real_frames = int(lens.sum())
@@ -320,6 +323,7 @@ def main():
                            "real_frames_per_gpu_step": real_frames, "parallelism": "dp%d" % world,
                            "recurrence": "persistent" if args.recurrence else "stepwise",
                            "gemm": "ffma" if args.ffma else "tcgen05_3xtf32",
+                           "frames_scale": args.frames_scale,
                            "l2": "working set per step (GBs of state buffers) exceeds the 126 MB L2; no flush needed"},
                 "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": in_b,
                         "d2h_bytes_per_step": 8},
