@@ -49,7 +49,7 @@ int LstmLayerImpl::create(const b2_lstm_desc &d) {
     if (!scratch) { own_scratch = new TcScratch; scratch = own_scratch; }
     B2_CUDA(cudaMalloc(&status_dev, sizeof(int)));
     B2_CUDA(cudaMemset(status_dev, 0, sizeof(int)));
-    size_t xw = lstm_persistent_xchg_words(els, d.parallel_sequences);
+    size_t xw = lstm_persistent_xchg_words(els, d.parallel_sequences, D);
     if (xw) {
         B2_CUDA(cudaMalloc(&xchg, xw * sizeof(unsigned long long)));
         B2_CUDA(cudaMemset(xchg, 0, xw * sizeof(unsigned long long)));   // tag 0 is never waited for

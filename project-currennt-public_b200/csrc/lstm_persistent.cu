@@ -22,9 +22,9 @@
 // Buffers are double-buffered over the step parity and over the item parity.
 //
 // Every wait is bounded: after SPIN_LIMIT polls (about a second) the thread records
-// B2_ERR_STEP_TIMEOUT in the layer's status word, raises the block's abort flag, and the block
-// leaves its loops without waiting again.  The host launches cooperatively so that all blocks of
-// a group are resident together.
+// B2_ERR_STEP_TIMEOUT in the layer's status word and sets its give-up flag; the next block barrier
+// ORs the flags (__syncthreads_or) and the block leaves its loops without waiting again.  The host
+// launches cooperatively so that all blocks of a group are resident together.
 #include "common.cuh"
 
 namespace b2 {
@@ -48,36 +48,41 @@ __device__ __forceinline__ int ld_status(const int *p) {
     asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(x) : "l"(p) : "memory");
     return x;
 }
-// bounded wait for a tagged value whose first look `x` did not carry the tag yet
-__device__ __noinline__ float wait_pair_slow(const u64 *p, unsigned tag, volatile int *abort_s, int *status) {
-    u64 x;
-    for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
-        if (*abort_s) return 0.0f;
-        x = ld_pair(p);
-        if ((unsigned)(x >> 32) == tag) return __uint_as_float((unsigned)x);
-        if ((it & 1023u) == 1023u && ld_status(status) != 0) break;  // another block gave up
-    }
-    *abort_s = 1;
-    atomicCAS(status, 0, (int)B2_ERR_STEP_TIMEOUT);
-    return 0.0f;
-}
-// Gather COUNT tagged values (thread-strided) into v[]: all loads are issued before the first tag
-// is examined, so the common case costs one L2 round trip, not one per value.
+// Gather COUNT tagged values (thread-strided) into v[].  Polling goes in ROUNDS: every round re-issues
+// the loads of all values that have not shown the tag yet and only then examines them, so a round
+// costs one L2 round trip no matter how many values a thread waits for.  Bounded: after SPIN_LIMIT
+// rounds (about a second), or when another block has reported a timeout, the thread records
+// B2_ERR_STEP_TIMEOUT, sets *gave_up and returns zeros.
 template <int COUNT>
 __device__ __forceinline__ void gather_pairs(float (&v)[(COUNT + NT - 1) / NT], const u64 *xb, unsigned tag, int tid,
-                                             volatile int *abort_s, int *status) {
+                                             int *gave_up, int *status) {
     constexpr int NW = (COUNT + NT - 1) / NT;
     u64 x[NW];
 #pragma unroll
-    for (int q = 0; q < NW; ++q) {
-        const int i = tid + q * NT;
-        x[q] = (COUNT % NT == 0 || i < COUNT) ? ld_pair(xb + i) : ((u64)tag << 32);
+    for (int q = 0; q < NW; ++q) x[q] = ~((u64)tag << 32);   // any word whose tag differs
+    if (!*gave_up) {
+        for (unsigned it = 0;; ++it) {
+#pragma unroll
+            for (int q = 0; q < NW; ++q) {
+                const int i = tid + q * NT;
+                if ((COUNT % NT == 0 || i < COUNT) && (unsigned)(x[q] >> 32) != tag) x[q] = ld_pair(xb + i);
+            }
+            bool all = true;
+#pragma unroll
+            for (int q = 0; q < NW; ++q) {
+                const int i = tid + q * NT;
+                if (COUNT % NT == 0 || i < COUNT) all = all && ((unsigned)(x[q] >> 32) == tag);
+            }
+            if (all) break;
+            if (it >= SPIN_LIMIT || ((it & 1023u) == 1023u && ld_status(status) != 0)) {
+                *gave_up = 1;
+                atomicCAS(status, 0, (int)B2_ERR_STEP_TIMEOUT);
+                break;
+            }
+        }
     }
 #pragma unroll
-    for (int q = 0; q < NW; ++q) {
-        if ((unsigned)(x[q] >> 32) == tag) v[q] = __uint_as_float((unsigned)x[q]);
-        else v[q] = wait_pair_slow(xb + tid + q * NT, tag, abort_s, status);
-    }
+    for (int q = 0; q < NW; ++q) v[q] = ((unsigned)(x[q] >> 32) == tag) ? __uint_as_float((unsigned)x[q]) : 0.0f;
 }
 
 struct PersistArgs {
@@ -120,7 +125,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
     constexpr int R = Gm::R, G = Gm::G, CELLS = Gm::CELLS, CPT = Gm::CPT, KSPLIT = Gm::KSPLIT, KPT = Gm::KPT;
     __shared__ __align__(16) float hs[ELS * PS];             // h[t-1] of the group's sequences, [k][p]
     __shared__ __align__(16) float red[KSPLIT * R * PS];     // k-split partial sums, [ks][r][p]
-    __shared__ int abort_s;
+    int gave_up = 0;   // this thread ran out of its wait budget; combined block-wide by __syncthreads_or
 
     const int tid = threadIdx.x;
     const int g = blockIdx.x % G, slot = blockIdx.x / G, nslots = gridDim.x / G;
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
     const int P = a.sh.P, T = a.sh.T, ls = a.sh.ls, D = a.sh.D;
     const LstmOffsets off = lstm_offsets(a.sh.pls, ls, ELS);
     u64 *xslot = a.xchg + (size_t)slot * 4 * ELS * PS;
-    if (tid == 0) abort_s = 0;
+
     __syncthreads();
 
     float wreg[KPT];
@@ -189,26 +194,30 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
             if (!first) {
                 const u64 *xb = xitem + (size_t)((s - 1) & 1) * ELS * PS;
                 float hv[(ELS * PS + NT - 1) / NT];
-                gather_pairs<ELS * PS>(hv, xb, tag0 + (unsigned)s, tid, &abort_s, a.status);
+                gather_pairs<ELS * PS>(hv, xb, tag0 + (unsigned)s, tid, &gave_up, a.status);
 #pragma unroll
                 for (int q = 0; q < (ELS * PS + NT - 1) / NT; ++q) {
                     const int i = tid + q * NT;
                     if ((ELS * PS) % NT == 0 || i < ELS * PS) hs[(i % ELS) * PS + (i / ELS)] = hv[q];
                 }
-                __syncthreads();
-                if (abort_s) { dead = true; break; }
+                const int dead_now = __syncthreads_or(gave_up);
+                if (dead_now) { dead = true; break; }
                 float acc[PS];
 #pragma unroll
                 for (int p = 0; p < PS; ++p) acc[p] = 0.0f;
-                if constexpr (PS == 4) {
-                    const float4 *h4 = reinterpret_cast<const float4 *>(hs) + ks * KPT;
+                if constexpr (PS % 4 == 0) {
+                    constexpr int Q = PS / 4;
+                    const float4 *h4 = reinterpret_cast<const float4 *>(hs) + ks * KPT * Q;
 #pragma unroll
                     for (int kk = 0; kk < KPT; ++kk) {
-                        const float4 h = h4[kk];
-                        acc[0] = fmaf(wreg[kk], h.x, acc[0]);
-                        acc[1 % PS] = fmaf(wreg[kk], h.y, acc[1 % PS]);
-                        acc[2 % PS] = fmaf(wreg[kk], h.z, acc[2 % PS]);
-                        acc[3 % PS] = fmaf(wreg[kk], h.w, acc[3 % PS]);
+#pragma unroll
+                        for (int q = 0; q < Q; ++q) {
+                            const float4 h = h4[kk * Q + q];
+                            acc[4 * q + 0] = fmaf(wreg[kk], h.x, acc[4 * q + 0]);
+                            acc[(4 * q + 1) % PS] = fmaf(wreg[kk], h.y, acc[(4 * q + 1) % PS]);
+                            acc[(4 * q + 2) % PS] = fmaf(wreg[kk], h.z, acc[(4 * q + 2) % PS]);
+                            acc[(4 * q + 3) % PS] = fmaf(wreg[kk], h.w, acc[(4 * q + 3) % PS]);
+                        }
                     }
                 } else {
                     const float4 *h4 = reinterpret_cast<const float4 *>(hs + ks * KPT);
@@ -288,7 +297,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
     __shared__ __align__(16) float pe2[NPART * CELLS];       // first-stage sums, [part][cell]
     __shared__ __align__(16) float ds[R * PS];               // this step's gate deltas, [r][p]
     __shared__ __align__(16) float redb[RSPLIT > 1 ? RSPLIT * ELS * PS : 1];
-    __shared__ int abort_s;
+    int gave_up = 0;
 
     const int tid = threadIdx.x;
     const int g = blockIdx.x % G, slot = blockIdx.x / G, nslots = gridDim.x / G;
@@ -299,7 +308,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
     constexpr size_t XBUF = (size_t)G * G * CELLS;
     u64 *xslot = a.xchg + (size_t)slot * 4 * XBUF;
     const int kcol = tid % ELS, rs = (ELS >= NT) ? 0 : tid / ELS;
-    if (tid == 0) abort_s = 0;
+
     __syncthreads();
 
     float wreg[CPTK][RPT];
@@ -365,14 +374,14 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
             if (!firstCall) {
                 const u64 *xb = xitem + (size_t)((s - 1) & 1) * XBUF + (size_t)g * G * CELLS;
                 float pv[(G * CELLS + NT - 1) / NT];
-                gather_pairs<G * CELLS>(pv, xb, tag0 + (unsigned)s, tid, &abort_s, a.status);
+                gather_pairs<G * CELLS>(pv, xb, tag0 + (unsigned)s, tid, &gave_up, a.status);
 #pragma unroll
                 for (int q = 0; q < (G * CELLS + NT - 1) / NT; ++q) {
                     const int i = tid + q * NT;
                     if ((G * CELLS) % NT == 0 || i < G * CELLS) pe[i] = pv[q];
                 }
-                __syncthreads();
-                if (abort_s) { dead = true; break; }
+                const int dead_now = __syncthreads_or(gave_up);
+                if (dead_now) { dead = true; break; }
                 if constexpr (CELLS <= NT) {
                     const int c = tid % CELLS, part = tid / CELLS;
                     float sum = 0.0f;
@@ -440,9 +449,12 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
             for (int rr = 0; rr < RPT; ++rr) {
                 const int row = rs * RPT + rr;
                 float dv[PS];
-                if constexpr (PS == 4) {
-                    const float4 v = reinterpret_cast<const float4 *>(ds)[row];
-                    dv[0] = v.x; dv[1 % PS] = v.y; dv[2 % PS] = v.z; dv[3 % PS] = v.w;
+                if constexpr (PS % 4 == 0) {
+#pragma unroll
+                    for (int q = 0; q < PS / 4; ++q) {
+                        const float4 v = reinterpret_cast<const float4 *>(ds)[row * (PS / 4) + q];
+                        dv[4 * q] = v.x; dv[(4 * q + 1) % PS] = v.y; dv[(4 * q + 2) % PS] = v.z; dv[(4 * q + 3) % PS] = v.w;
+                    }
                 } else {
 #pragma unroll
                     for (int p = 0; p < PS; ++p) dv[p] = ds[row * PS + p];
@@ -520,10 +532,26 @@ bool persistent_geometry(int els, int *JB) {
     }
 }
 
-size_t lstm_persistent_xchg_words(int els, int P) {
+// Sequences per work item.  More sequences per item amortise the per-step exchange latency over more
+// work; fewer items than group slots leave SMs idle.  Take the smallest PS that lets every item have a
+// slot of its own, else the largest the register budget of the geometry allows.
+int persistent_ps(int els, int P, int D) {
     int JB;
     if (!persistent_geometry(els, &JB)) return 0;
-    const int PS = P == 1 ? 1 : 4, G = els / JB;
+    if (P == 1) return 1;
+    const int G = els / JB;
+    int slots = num_sms() / G;
+    if (slots < 1) slots = 1;
+    const int max_ps = els >= 1024 ? 8 : 16;
+    for (int ps = 4; ps <= max_ps; ps *= 2)
+        if (D * ((P + ps - 1) / ps) <= slots) return ps;
+    return max_ps;
+}
+
+size_t lstm_persistent_xchg_words(int els, int P, int D) {
+    int JB;
+    if (!persistent_geometry(els, &JB)) return 0;
+    const int PS = persistent_ps(els, P, D), G = els / JB;
     int max_slots = num_sms() / G;
     if (max_slots < 1) max_slots = 1;
     size_t fwd = (size_t)4 * els * PS, bwd = (size_t)4 * G * G * JB * PS;
@@ -538,21 +566,27 @@ int lstm_persistent(bool backward, const LstmShape &s, const LstmBuffers &b, con
     PersistArgs a;
     a.sh = s; a.bf = b; a.w = w; a.y = y; a.dy = dy; a.xchg = xchg; a.status = status;
     a.tag_base = *tag_next;
-    const int PS = s.P == 1 ? 1 : 4;
+    const int PS = persistent_ps(s.els, s.P, s.D);
     a.n_items = s.D * ((s.P + PS - 1) / PS);
-    int ips = 1, rc;
-#define CASE(E, J)                                                                   \
-    case E:                                                                          \
-        rc = PS == 1 ? launch<E, J, 1>(backward, a, st, &ips) : launch<E, J, 4>(backward, a, st, &ips); \
+    int ips = 1, rc = 1;
+#define CASE_PS(E, J, Q) \
+    case Q: rc = launch<E, J, Q>(backward, a, st, &ips); break;
+#define CASE(E, J, WITH16)                                       \
+    case E:                                                      \
+        switch (PS) {                                            \
+            CASE_PS(E, J, 1) CASE_PS(E, J, 4) CASE_PS(E, J, 8) WITH16 \
+            default: return 1;                                   \
+        }                                                        \
         break;
     switch (s.els) {
-        CASE(1024, 8)
-        CASE(512, 16)
-        CASE(256, 32)
-        CASE(128, 64)
+        CASE(1024, 8, )
+        CASE(512, 16, CASE_PS(512, 16, 16))
+        CASE(256, 32, CASE_PS(256, 32, 16))
+        CASE(128, 64, CASE_PS(128, 64, 16))
         default: return 1;
     }
 #undef CASE
+#undef CASE_PS
     if (rc == B2_OK) *tag_next += (unsigned)ips * (unsigned)(s.T + 1) + 1u;
     return rc;
 }

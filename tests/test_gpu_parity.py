@@ -116,7 +116,9 @@ def test_config_layer_sizes_reduced_frames(cfg, P, scale, variant):
 
 @pytest.mark.parametrize("variant", VARIANTS[1:3], ids=VARIANT_IDS[1:3])
 @pytest.mark.parametrize("ls,bi,P,lens", [(2048, 1, 5, [12, 12, 7, 3, 12]), (1024, 0, 1, [9]), (256, 1, 9, [14] * 9),
-                                          (512, 1, 2, [6, 11]), (256, 0, 7, [10, 9, 8, 7, 6, 5, 4])])
+                                          (512, 1, 2, [6, 11]), (256, 0, 7, [10, 9, 8, 7, 6, 5, 4]),
+                                          (512, 1, 40, [7] * 20 + [5] * 19 + [2]), (512, 1, 83, [5] * 80 + [3, 2, 1]),
+                                          (1024, 1, 9, [6] * 8 + [4]), (1024, 1, 21, [5] * 21), (256, 1, 150, [3] * 150)])
 def test_persistent_geometries(ls, bi, P, lens, variant):
     """Every register-resident geometry of the persistent kernels (128/256/512/1024 units per
     direction, 1 or 4 sequences per group, sequence counts that do not fill the last group)."""
