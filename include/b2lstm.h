@@ -106,7 +106,10 @@ int b2_lstm_forward(b2_lstm *layer, const float *weights_dev, const float *x_dev
  * nobody reads); dw_dev: weightUpdates(), OVERWRITTEN, same layout as the weights. */
 int b2_lstm_backward(b2_lstm *layer, const float *weights_dev, const float *x_dev, const float *y_dev,
                      const float *dy_dev, float *dx_dev, float *dw_dev, b2_stream stream);
-/* Which recurrence kernels run: 0 = one launch per timestep, 1 = persistent kernel (default). */
+/* Which recurrence kernels run: 0 = one launch per timestep; 1 = persistent kernel exchanging
+ * through L2 (default; measured fastest on B200); 2 = persistent kernel exchanging through
+ * distributed shared memory where a group fits a thread-block cluster (128 or 256 units per
+ * direction), through L2 otherwise. */
 int b2_lstm_set_recurrence_mode(b2_lstm *layer, int mode);
 /* Waits for the work enqueued on `stream` and reports what the layer's kernels recorded:
  * B2_ERR_STEP_TIMEOUT if a persistent kernel gave up a bounded wait, else B2_OK. */
@@ -179,7 +182,8 @@ int b2_net_get_output_errors(b2_net *net, int layer, float *host_out);
 int b2_net_synchronize(b2_net *net);
 /* The stream all of the net's work is ordered on (a cudaStream_t). */
 b2_stream b2_net_stream(b2_net *net);
-/* 0 = stepwise recurrence kernels, 1 = persistent (default); applies to every (b)lstm layer. */
+/* 0 = stepwise recurrence kernels, 1 = persistent (default), 2 = persistent with cluster exchange;
+ * applies to every (b)lstm layer (see b2_lstm_set_recurrence_mode). */
 int b2_net_set_recurrence_mode(b2_net *net, int mode);
 /* Non-zero forces the FFMA GEMM everywhere (the tensor-core GEMM is the default). */
 int b2_net_set_force_ffma(b2_net *net, int on);

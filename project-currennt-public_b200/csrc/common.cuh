@@ -127,9 +127,10 @@ int lstm_vector_grads(const LstmShape &s, const LstmBuffers &b, float *dw, float
 // persistent kernels (lstm_persistent.cu).  Return B2_OK, an error, or 1 when the shape has no
 // persistent kernel (the caller then uses the stepwise kernels).
 size_t lstm_persistent_xchg_words(int els, int P, int D);
-int persistent_ps(int els, int P, int D);   // sequences per work item chosen for a shape (0: no persistent kernel)
-int lstm_persistent(bool backward, const LstmShape &s, const LstmBuffers &b, const float *w, float *y, const float *dy,
-                    unsigned long long *xchg, int *status, unsigned *tag_next, cudaStream_t st);
+int persistent_ps(int els, int P, int D, bool use_cluster);   // sequences per work item for a shape (0: no persistent kernel)
+// use_cluster: groups of <= 8 blocks exchange through distributed shared memory (thread-block clusters)
+int lstm_persistent(bool backward, bool use_cluster, const LstmShape &s, const LstmBuffers &b, const float *w, float *y,
+                    const float *dy, unsigned long long *xchg, int *status, unsigned *tag_next, cudaStream_t st);
 
 // offsets inside the (b)lstm weight vector
 struct LstmOffsets {

@@ -102,7 +102,7 @@ int LstmLayerImpl::forward(const float *w, const float *x, float *y, cudaStream_
     {
         Phase ph(*this, "lstm_fwd_recurrence");
         B2_TRY(lstm_prepare_wrecT(s, w, bufs.wrecT, st));
-        int rc = recurrence_mode == 1 ? lstm_persistent(false, s, bufs, w, y, nullptr, xchg, status_dev, &tag_next, st) : 1;
+        int rc = recurrence_mode >= 1 ? lstm_persistent(false, recurrence_mode == 2, s, bufs, w, y, nullptr, xchg, status_dev, &tag_next, st) : 1;
         if (rc == 1) rc = lstm_forward_stepwise(s, bufs, w, y, st);
         B2_TRY(rc);
     }
@@ -119,7 +119,7 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
     const LstmOffsets off = lstm_offsets(pls, ls, els);
     {
         Phase ph(*this, "lstm_bwd_recurrence");
-        int rc = recurrence_mode == 1 ? lstm_persistent(true, s, bufs, w, nullptr, dy, xchg, status_dev, &tag_next, st) : 1;
+        int rc = recurrence_mode >= 1 ? lstm_persistent(true, recurrence_mode == 2, s, bufs, w, nullptr, dy, xchg, status_dev, &tag_next, st) : 1;
         if (rc == 1) rc = lstm_backward_stepwise(s, bufs, w, dy, st);
         B2_TRY(rc);
     }

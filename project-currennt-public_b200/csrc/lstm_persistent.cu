@@ -16,15 +16,32 @@
 //             unit k (same weight slice, other contraction index) and sends each partial to the
 //             block that owns k, which adds the G partials in a fixed order -> reduce-scatter
 //
-// Exchange through L2 with the flag inside the datum: a value travels as one naturally aligned
-// 64-bit word {step tag : float bits}, written with st.relaxed.gpu and polled with
-// ld.relaxed.gpu, so one L2 round trip delivers both "ready" and the value; no fence, no atomics.
-// Buffers are double-buffered over the step parity and over the item parity.
+// Register tiles.  The per-step products read their vector operand (h[t-1] resp. the gate deltas)
+// from shared memory as warp-wide broadcasts, which deliver only 16 bytes per 4 shared-memory
+// cycles.  Each thread therefore multiplies every value it loads with FOUR weights:
+//   forward : thread = (unit jj, k-range of 32): the 4 gate rows of its unit x 32 source units
+//   backward: thread = (4 adjacent source units k, 32 of the block's gate rows)
+// so that a step needs 32 broadcast loads per thread and sequence quad instead of 128; the partial
+// sums of the k-ranges (row ranges) are combined through shared memory.
 //
-// Every wait is bounded: after SPIN_LIMIT polls (about a second) the thread records
-// B2_ERR_STEP_TIMEOUT in the layer's status word and sets its give-up flag; the next block barrier
-// ORs the flags (__syncthreads_or) and the block leaves its loops without waiting again.  The host
-// launches cooperatively so that all blocks of a group are resident together.
+// Exchange.  Two transports, same data flow:
+//  * thread-block cluster (groups of <= 8 blocks: 128 or 256 units per direction): values are stored
+//    straight into the peers' shared memory (distributed shared memory, st.shared::cluster) and one
+//    hardware cluster barrier (arrive.release / wait.acquire) per step orders them;
+//  * L2 (any group size): the flag travels inside the datum: one naturally aligned 64-bit word
+//    {step tag : float bits}, written with st.relaxed.gpu and polled with ld.relaxed.gpu, so one L2
+//    round trip delivers both "ready" and the value; no fence, no atomics.  Polling goes in rounds
+//    (all outstanding loads are issued before any is examined).  Buffers are double-buffered over
+//    the step parity and over the item parity.
+//
+// Every software wait is bounded: after SPIN_LIMIT polling rounds (about a second) the thread
+// records B2_ERR_STEP_TIMEOUT in the layer's status word and sets its give-up flag; the next block
+// barrier ORs the flags (__syncthreads_or) and the block leaves its loops without waiting again.
+// The L2 variant is launched cooperatively so that all blocks of a group are resident together;
+// clusters are co-scheduled by the hardware.
+#include <cstdio>
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace b2 {
@@ -85,13 +102,26 @@ __device__ __forceinline__ void gather_pairs(float (&v)[(COUNT + NT - 1) / NT], 
     for (int q = 0; q < NW; ++q) v[q] = ((unsigned)(x[q] >> 32) == tag) ? __uint_as_float((unsigned)x[q]) : 0.0f;
 }
 
+// ---- thread-block cluster exchange
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_remote(uint32_t raddr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(raddr), "f"(v) : "memory");
+}
+
 struct PersistArgs {
     LstmShape sh;
     LstmBuffers bf;
     const float *w;
     float *y;          // forward: block outputs (written); backward: unused
     const float *dy;   // backward: output errors (read)
-    u64 *xchg;         // exchange buffers, per slot
+    u64 *xchg;         // exchange buffers, per slot (L2 transport)
     int *status;       // 0 ok, else an error code
     unsigned tag_base;
     int n_items;       // D * ceil(P / PS)
@@ -103,42 +133,57 @@ struct Geo {
     static constexpr int G = ELS / JB;               // blocks per group
     static constexpr int CELLS = JB * PS;            // (unit, sequence) cells owned by a block
     static constexpr int CPT = (CELLS + NT - 1) / NT;
-    // forward: thread = (row r, k-split ks), weights W[r][ks*KPT .. +KPT)
-    static constexpr int KSPLIT = NT / R;
+    static constexpr int PC = PS < 8 ? PS : 8;       // sequences per accumulation pass (register budget)
+    // forward: thread = (unit jj, k-split ks): weights W[4 gates of jj][ks*KPT .. +KPT)
+    static constexpr int KSPLIT = NT / JB;
     static constexpr int KPT = ELS / KSPLIT;
-    // backward: thread = (columns k, row-split rs), weights W[rs*RPT .. +RPT)[k]
-    static constexpr int CPTK = ELS >= NT ? ELS / NT : 1;
-    static constexpr int RSPLIT = ELS >= NT ? 1 : NT / ELS;
+    // backward: thread = (k-quad kq, row-split rs): weights W[rs*RPT .. +RPT)[4*kq .. +4)
+    static constexpr int KQ = ELS / 4;
+    static constexpr int RSPLIT = NT / KQ;
     static constexpr int RPT = R / RSPLIT;
     static constexpr int NPART = NT / CELLS >= 1 ? NT / CELLS : 1;   // threads per cell when summing partials
-    static_assert(R <= NT && NT % R == 0 && ELS % KSPLIT == 0 && ELS % JB == 0, "bad geometry");
-    static_assert(KPT <= 128 && CPTK * RPT <= 128, "weight slice does not fit the register budget");
+    static_assert(NT % JB == 0 && ELS % KSPLIT == 0 && ELS % JB == 0 && 4 * KPT <= 128, "bad forward geometry");
+    static_assert(ELS % 4 == 0 && NT % KQ == 0 && R % RSPLIT == 0 && 4 * RPT <= 128, "bad backward geometry");
     static_assert(CELLS <= NT ? NT % CELLS == 0 : CELLS % NT == 0, "cells must tile the block");
+    // dynamic shared memory, in floats
+    static constexpr int FWD_HS = ELS * PS, FWD_RED = NT * 4 * PS;
+    static constexpr int BWD_PE = ELS * PS, BWD_PE2 = NT, BWD_DS = R * PS, BWD_REDB = RSPLIT * ELS * PS;
+    // forward: when the block owns few cells, the k-split partial sums are first combined by all threads
+    static constexpr int NPARTF = (4 * CELLS < NT) ? NT / (4 * CELLS) : 1;
+    static constexpr int FWD_RED2 = NPARTF > 1 ? NT : 4;
+    static_assert(KSPLIT % NPARTF == 0, "k-splits must divide over the reduce parts");
+    static constexpr size_t fwd_smem(bool cl) { return sizeof(float) * ((cl ? 2 : 1) * FWD_HS + FWD_RED + FWD_RED2); }
+    static constexpr size_t bwd_smem(bool cl) { return sizeof(float) * ((cl ? 2 : 1) * BWD_PE + BWD_PE2 + BWD_DS + BWD_REDB); }
 };
+
+extern __shared__ __align__(16) float smem_dyn[];
 
 // =================================================================================================
 // forward
 // =================================================================================================
-template <int ELS, int JB, int PS>
+template <int ELS, int JB, int PS, bool CL>
 __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs a) {
     typedef Geo<ELS, JB, PS> Gm;
-    constexpr int R = Gm::R, G = Gm::G, CELLS = Gm::CELLS, CPT = Gm::CPT, KSPLIT = Gm::KSPLIT, KPT = Gm::KPT;
-    __shared__ __align__(16) float hs[ELS * PS];             // h[t-1] of the group's sequences, [k][p]
-    __shared__ __align__(16) float red[KSPLIT * R * PS];     // k-split partial sums, [ks][r][p]
+    constexpr int G = Gm::G, CELLS = Gm::CELLS, CPT = Gm::CPT, KSPLIT = Gm::KSPLIT, KPT = Gm::KPT, PC = Gm::PC;
+    // h[t-1] of the group's sequences, [k][p]; with clusters the peers write it directly, double-buffered
+    float *hs_all = smem_dyn;
+    // k-split partial sums of the gate pre-activations, [ks][gate][p][jj]
+    float *red = smem_dyn + (CL ? 2 : 1) * Gm::FWD_HS;
+    float *red2 = red + Gm::FWD_RED;   // [part][gate][p][jj], only when NPARTF > 1
+    constexpr int NPARTF = Gm::NPARTF;
     int gave_up = 0;   // this thread ran out of its wait budget; combined block-wide by __syncthreads_or
 
     const int tid = threadIdx.x;
     const int g = blockIdx.x % G, slot = blockIdx.x / G, nslots = gridDim.x / G;
-    const int r = tid % R, ks = tid / R;
-    const int gate_r = r / JB, jj_r = r % JB;
+    const int jj_f = tid % JB, ks = tid / JB;
     const int j0 = g * JB;
     const int P = a.sh.P, T = a.sh.T, ls = a.sh.ls, D = a.sh.D;
     const LstmOffsets off = lstm_offsets(a.sh.pls, ls, ELS);
     u64 *xslot = a.xchg + (size_t)slot * 4 * ELS * PS;
+    // a peer's shared memory may only be touched once that peer has started running
+    if constexpr (CL) { cluster_arrive(); cluster_wait(); }
 
-    __syncthreads();
-
-    float wreg[KPT];
+    float wreg[4][KPT];
     int cur_d = -1;
     for (int item = slot; item < a.n_items; item += nslots) {
         const int d = item % D, p0 = (item / D) * PS, seq = item / nslots;
@@ -146,8 +191,10 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
             // W_rec[gate][d][j0+jj][k] from the source-major copy [d][k][gate][j] (coalesced over j)
             const float *wt = a.bf.wrecT + (size_t)d * ELS * 4 * ELS;
 #pragma unroll
-            for (int kk = 0; kk < KPT; ++kk)
-                wreg[kk] = __ldg(wt + ((size_t)(ks * KPT + kk) * 4 + gate_r) * ELS + j0 + jj_r);
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int kk = 0; kk < KPT; ++kk)
+                    wreg[q][kk] = __ldg(wt + ((size_t)(ks * KPT + kk) * 4 + q) * ELS + j0 + jj_f);
             cur_d = d;
         }
         const unsigned tag0 = a.tag_base + (unsigned)seq * (unsigned)(T + 1);
@@ -190,51 +237,66 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
                     }
                 }
             }
-            // 2. gather h[t-1] of the whole group, 3. recurrent projection with register-resident weights
+            // 2. h[t-1] of the whole group, 3. recurrent projection with register-resident weights
             if (!first) {
-                const u64 *xb = xitem + (size_t)((s - 1) & 1) * ELS * PS;
-                float hv[(ELS * PS + NT - 1) / NT];
-                gather_pairs<ELS * PS>(hv, xb, tag0 + (unsigned)s, tid, &gave_up, a.status);
+                const float *hs = hs_all;
+                if constexpr (CL) {
+                    cluster_wait();   // every block of the cluster has stored its h[t-1] (release/acquire)
+                    hs = hs_all + ((s - 1) & 1) * ELS * PS;
+                } else {
+                    const u64 *xb = xitem + (size_t)((s - 1) & 1) * ELS * PS;
+                    float hv[(ELS * PS + NT - 1) / NT];
+                    gather_pairs<ELS * PS>(hv, xb, tag0 + (unsigned)s, tid, &gave_up, a.status);
 #pragma unroll
-                for (int q = 0; q < (ELS * PS + NT - 1) / NT; ++q) {
-                    const int i = tid + q * NT;
-                    if ((ELS * PS) % NT == 0 || i < ELS * PS) hs[(i % ELS) * PS + (i / ELS)] = hv[q];
+                    for (int q = 0; q < (ELS * PS + NT - 1) / NT; ++q) {
+                        const int i = tid + q * NT;
+                        if ((ELS * PS) % NT == 0 || i < ELS * PS) hs_all[(i % ELS) * PS + (i / ELS)] = hv[q];
+                    }
+                    const int dead_now = __syncthreads_or(gave_up);
+                    if (dead_now) { dead = true; break; }
                 }
-                const int dead_now = __syncthreads_or(gave_up);
-                if (dead_now) { dead = true; break; }
-                float acc[PS];
+#pragma unroll 1
+                for (int pc0 = 0; pc0 < PS; pc0 += PC) {
+                    float acc[4][PC];
 #pragma unroll
-                for (int p = 0; p < PS; ++p) acc[p] = 0.0f;
-                if constexpr (PS % 4 == 0) {
-                    constexpr int Q = PS / 4;
-                    const float4 *h4 = reinterpret_cast<const float4 *>(hs) + ks * KPT * Q;
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int p = 0; p < PC; ++p) acc[q][p] = 0.0f;
 #pragma unroll
                     for (int kk = 0; kk < KPT; ++kk) {
+                        float hvv[PC];
+                        const float *hp = hs + (ks * KPT + kk) * PS + pc0;
+                        if constexpr (PC % 4 == 0) {
 #pragma unroll
-                        for (int q = 0; q < Q; ++q) {
-                            const float4 h = h4[kk * Q + q];
-                            acc[4 * q + 0] = fmaf(wreg[kk], h.x, acc[4 * q + 0]);
-                            acc[(4 * q + 1) % PS] = fmaf(wreg[kk], h.y, acc[(4 * q + 1) % PS]);
-                            acc[(4 * q + 2) % PS] = fmaf(wreg[kk], h.z, acc[(4 * q + 2) % PS]);
-                            acc[(4 * q + 3) % PS] = fmaf(wreg[kk], h.w, acc[(4 * q + 3) % PS]);
+                            for (int p4 = 0; p4 < PC / 4; ++p4) {
+                                const float4 h4 = reinterpret_cast<const float4 *>(hp)[p4];
+                                hvv[4 * p4] = h4.x; hvv[(4 * p4 + 1) % PC] = h4.y;
+                                hvv[(4 * p4 + 2) % PC] = h4.z; hvv[(4 * p4 + 3) % PC] = h4.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int p = 0; p < PC; ++p) hvv[p] = hp[p];
                         }
-                    }
-                } else {
-                    const float4 *h4 = reinterpret_cast<const float4 *>(hs + ks * KPT);
-                    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-                    for (int kk = 0; kk < KPT; kk += 4) {
-                        const float4 h = h4[kk / 4];
-                        a0 = fmaf(wreg[kk], h.x, a0);
-                        a1 = fmaf(wreg[kk + 1], h.y, a1);
-                        a2 = fmaf(wreg[kk + 2], h.z, a2);
-                        a3 = fmaf(wreg[kk + 3], h.w, a3);
+                        for (int q = 0; q < 4; ++q)
+#pragma unroll
+                            for (int p = 0; p < PC; ++p) acc[q][p] = fmaf(wreg[q][kk], hvv[p], acc[q][p]);
                     }
-                    acc[0] = (a0 + a1) + (a2 + a3);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int p = 0; p < PC; ++p) red[((ks * 4 + q) * PS + pc0 + p) * JB + jj_f] = acc[q][p];
                 }
-#pragma unroll
-                for (int p = 0; p < PS; ++p) red[(ks * R + r) * PS + p] = acc[p];
                 __syncthreads();
+                if constexpr (NPARTF > 1) {
+                    // 4*CELLS gate sums, NPARTF threads each: thread = (part, output o = (gate*PS + p)*JB + jj)
+                    const int o = tid % (4 * CELLS), part = tid / (4 * CELLS);
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int k2 = 0; k2 < KSPLIT / NPARTF; ++k2) sum += red[(part * (KSPLIT / NPARTF) + k2) * 4 * CELLS + o];
+                    red2[part * 4 * CELLS + o] = sum;
+                    __syncthreads();
+                }
             }
             // 4. gate math, state update, publish h[t]
             u64 *xo = xitem + (size_t)(s & 1) * ELS * PS;
@@ -255,10 +317,17 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
                     } else {
                         float rec[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                         if (!first) {
+                            if constexpr (NPARTF > 1) {
 #pragma unroll
-                            for (int q = 0; q < 4; ++q)
+                                for (int q = 0; q < 4; ++q)
 #pragma unroll
-                                for (int k2 = 0; k2 < KSPLIT; ++k2) rec[q] += red[(k2 * R + q * JB + jj) * PS + p];
+                                    for (int k2 = 0; k2 < NPARTF; ++k2) rec[q] += red2[k2 * 4 * CELLS + (q * PS + p) * JB + jj];
+                            } else {
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+#pragma unroll 8
+                                    for (int k2 = 0; k2 < KSPLIT; ++k2) rec[q] += red[((k2 * 4 + q) * PS + p) * JB + jj];
+                            }
                         }
                         float ni = a4[ci][0] + rec[0] + b4[ci][0];
                         float ig = a4[ci][1] + rec[1] + b4[ci][1];
@@ -277,9 +346,19 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
                     }
                     a.y[f * ls + u] = h;
                 }
-                st_pair(xo + (size_t)p * ELS + j0 + jj, h, tag0 + (unsigned)s + 1u);
+                if constexpr (CL) {
+                    const uint32_t la = smem_addr(hs_all + (s & 1) * ELS * PS + (j0 + jj) * PS + p);
+#pragma unroll
+                    for (int rk = 0; rk < G; ++rk) st_remote(map_to_rank(la, (uint32_t)rk), h);
+                } else {
+                    st_pair(xo + (size_t)p * ELS + j0 + jj, h, tag0 + (unsigned)s + 1u);
+                }
             }
+            if constexpr (CL) cluster_arrive();
         }
+        // the last arrive of the item is matched here; it also keeps a fast block from overwriting
+        // buffers (or leaving the kernel) while a peer still reads them
+        if constexpr (CL) { if (T > 0) cluster_wait(); }
         if (dead) break;
     }
 }
@@ -287,16 +366,17 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
 // =================================================================================================
 // backward
 // =================================================================================================
-template <int ELS, int JB, int PS>
+template <int ELS, int JB, int PS, bool CL>
 __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs a) {
     typedef Geo<ELS, JB, PS> Gm;
-    constexpr int R = Gm::R, G = Gm::G, CELLS = Gm::CELLS, CPT = Gm::CPT;
-    constexpr int CPTK = Gm::CPTK, RSPLIT = Gm::RSPLIT, RPT = Gm::RPT, NPART = Gm::NPART;
+    constexpr int G = Gm::G, CELLS = Gm::CELLS, CPT = Gm::CPT, PC = Gm::PC;
+    constexpr int KQ = Gm::KQ, RSPLIT = Gm::RSPLIT, RPT = Gm::RPT, NPART = Gm::NPART;
     constexpr int SRC_PER_PART = (G + NPART - 1) / NPART;
-    __shared__ __align__(16) float pe[G * CELLS];            // partial sums received, [src][cell]
-    __shared__ __align__(16) float pe2[NPART * CELLS];       // first-stage sums, [part][cell]
-    __shared__ __align__(16) float ds[R * PS];               // this step's gate deltas, [r][p]
-    __shared__ __align__(16) float redb[RSPLIT > 1 ? RSPLIT * ELS * PS : 1];
+    // partial sums received, [src][cell]; with clusters the peers write them directly, double-buffered
+    float *pe_all = smem_dyn;
+    float *pe2 = pe_all + (CL ? 2 : 1) * Gm::BWD_PE;   // first-stage sums, [part][cell]
+    float *ds = pe2 + Gm::BWD_PE2;                      // this step's gate deltas, [row][p]
+    float *redb = ds + Gm::BWD_DS;                      // row-split partial sums, [rs][p][k]
     int gave_up = 0;
 
     const int tid = threadIdx.x;
@@ -307,23 +387,23 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
     // one exchange buffer holds, per owner block, G source blocks x CELLS tagged partial sums
     constexpr size_t XBUF = (size_t)G * G * CELLS;
     u64 *xslot = a.xchg + (size_t)slot * 4 * XBUF;
-    const int kcol = tid % ELS, rs = (ELS >= NT) ? 0 : tid / ELS;
+    const int kq = tid % KQ, rs = tid / KQ;
+    // a peer's shared memory may only be touched once that peer has started running
+    if constexpr (CL) { cluster_arrive(); cluster_wait(); }
 
-    __syncthreads();
-
-    float wreg[CPTK][RPT];
+    float wreg[4][RPT];
     int cur_d = -1;
     for (int item = slot; item < a.n_items; item += nslots) {
         const int d = item % D, p0 = (item / D) * PS, seq = item / nslots;
         if (d != cur_d) {
-            // W_rec[gate][d][j0+jj][k], row r = gate*JB + jj; consecutive threads read consecutive k
+            // W_rec[gate][d][j0+jj][k], row = gate*JB + jj, this thread's columns k = 4*kq .. 4*kq+3
 #pragma unroll
-            for (int c = 0; c < CPTK; ++c)
+            for (int rr = 0; rr < RPT; ++rr) {
+                const int row = rs * RPT + rr;
+                const float *wp = a.w + off.rec + ((size_t)(row / JB) * ls + (size_t)d * ELS + j0 + (row % JB)) * ELS + 4 * kq;
 #pragma unroll
-                for (int rr = 0; rr < RPT; ++rr) {
-                    const int row = rs * RPT + rr, k = (ELS >= NT) ? tid + c * NT : kcol;
-                    wreg[c][rr] = __ldg(a.w + off.rec + ((size_t)(row / JB) * ls + (size_t)d * ELS + j0 + (row % JB)) * ELS + k);
-                }
+                for (int c = 0; c < 4; ++c) wreg[c][rr] = __ldg(wp + c);
+            }
             cur_d = d;
         }
         const unsigned tag0 = a.tag_base + (unsigned)seq * (unsigned)(T + 1);
@@ -371,17 +451,23 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
                 }
             }
             // 2. partial sums of the recurrent error from every block of the group
+            const float *pe = pe_all;
             if (!firstCall) {
-                const u64 *xb = xitem + (size_t)((s - 1) & 1) * XBUF + (size_t)g * G * CELLS;
-                float pv[(G * CELLS + NT - 1) / NT];
-                gather_pairs<G * CELLS>(pv, xb, tag0 + (unsigned)s, tid, &gave_up, a.status);
+                if constexpr (CL) {
+                    cluster_wait();   // every block of the cluster has stored its partial sums (release/acquire)
+                    pe = pe_all + ((s - 1) & 1) * G * CELLS;
+                } else {
+                    const u64 *xb = xitem + (size_t)((s - 1) & 1) * XBUF + (size_t)g * G * CELLS;
+                    float pv[(G * CELLS + NT - 1) / NT];
+                    gather_pairs<G * CELLS>(pv, xb, tag0 + (unsigned)s, tid, &gave_up, a.status);
 #pragma unroll
-                for (int q = 0; q < (G * CELLS + NT - 1) / NT; ++q) {
-                    const int i = tid + q * NT;
-                    if ((G * CELLS) % NT == 0 || i < G * CELLS) pe[i] = pv[q];
+                    for (int q = 0; q < (G * CELLS + NT - 1) / NT; ++q) {
+                        const int i = tid + q * NT;
+                        if ((G * CELLS) % NT == 0 || i < G * CELLS) pe_all[i] = pv[q];
+                    }
+                    const int dead_now = __syncthreads_or(gave_up);
+                    if (dead_now) { dead = true; break; }
                 }
-                const int dead_now = __syncthreads_or(gave_up);
-                if (dead_now) { dead = true; break; }
                 if constexpr (CELLS <= NT) {
                     const int c = tid % CELLS, part = tid / CELLS;
                     float sum = 0.0f;
@@ -440,53 +526,64 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
             if (lastCall) break;
             __syncthreads();
             // 4. this block's contribution to the output error of every unit k at the next step
-            float acc[CPTK][PS];
-#pragma unroll
-            for (int c = 0; c < CPTK; ++c)
-#pragma unroll
-                for (int p = 0; p < PS; ++p) acc[c][p] = 0.0f;
-#pragma unroll
-            for (int rr = 0; rr < RPT; ++rr) {
-                const int row = rs * RPT + rr;
-                float dv[PS];
-                if constexpr (PS % 4 == 0) {
-#pragma unroll
-                    for (int q = 0; q < PS / 4; ++q) {
-                        const float4 v = reinterpret_cast<const float4 *>(ds)[row * (PS / 4) + q];
-                        dv[4 * q] = v.x; dv[(4 * q + 1) % PS] = v.y; dv[(4 * q + 2) % PS] = v.z; dv[(4 * q + 3) % PS] = v.w;
-                    }
-                } else {
-#pragma unroll
-                    for (int p = 0; p < PS; ++p) dv[p] = ds[row * PS + p];
-                }
-#pragma unroll
-                for (int c = 0; c < CPTK; ++c)
-#pragma unroll
-                    for (int p = 0; p < PS; ++p) acc[c][p] = fmaf(wreg[c][rr], dv[p], acc[c][p]);
-            }
             u64 *xo = xitem + (size_t)(s & 1) * XBUF;
             const unsigned tag = tag0 + (unsigned)s + 1u;
-            if constexpr (RSPLIT > 1) {
+            // where partial (k, p) of this source block goes: into the owner's [src][cell] buffer
+            auto send = [&](int k, int p, float v) {
+                const int cell = p * JB + (k % JB);
+                if constexpr (CL)
+                    st_remote(map_to_rank(smem_addr(pe_all + ((s & 1) * G + g) * CELLS + cell), (uint32_t)(k / JB)), v);
+                else
+                    st_pair(xo + ((size_t)(k / JB) * G + g) * CELLS + cell, v, tag);
+            };
+#pragma unroll 1
+            for (int pc0 = 0; pc0 < PS; pc0 += PC) {
+                float acc[4][PC];
 #pragma unroll
-                for (int p = 0; p < PS; ++p) redb[(rs * ELS + kcol) * PS + p] = acc[0][p];
-                __syncthreads();
-                for (int i = tid; i < ELS * PS; i += NT) {
-                    const int k = i % ELS, p = i / ELS;
-                    float v = 0.0f;
+                for (int c = 0; c < 4; ++c)
 #pragma unroll
-                    for (int q = 0; q < RSPLIT; ++q) v += redb[(q * ELS + k) * PS + p];
-                    st_pair(xo + ((size_t)(k / JB) * G + g) * CELLS + p * JB + (k % JB), v, tag);
+                    for (int p = 0; p < PC; ++p) acc[c][p] = 0.0f;
+#pragma unroll
+                for (int rr = 0; rr < RPT; ++rr) {
+                    float dv[PC];
+                    const float *dp = ds + (rs * RPT + rr) * PS + pc0;
+                    if constexpr (PC % 4 == 0) {
+#pragma unroll
+                        for (int p4 = 0; p4 < PC / 4; ++p4) {
+                            const float4 v4 = reinterpret_cast<const float4 *>(dp)[p4];
+                            dv[4 * p4] = v4.x; dv[(4 * p4 + 1) % PC] = v4.y;
+                            dv[(4 * p4 + 2) % PC] = v4.z; dv[(4 * p4 + 3) % PC] = v4.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int p = 0; p < PC; ++p) dv[p] = dp[p];
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int p = 0; p < PC; ++p) acc[c][p] = fmaf(wreg[c][rr], dv[p], acc[c][p]);
                 }
-            } else {
 #pragma unroll
-                for (int c = 0; c < CPTK; ++c) {
-                    const int k = tid + c * NT;
-#pragma unroll
-                    for (int p = 0; p < PS; ++p)
-                        st_pair(xo + ((size_t)(k / JB) * G + g) * CELLS + p * JB + (k % JB), acc[c][p], tag);
-                }
+                for (int p = 0; p < PC; ++p)
+                    *reinterpret_cast<float4 *>(redb + ((size_t)(rs * PS + pc0 + p) * ELS + 4 * kq)) =
+                        make_float4(acc[0][p], acc[1][p], acc[2][p], acc[3][p]);
             }
+            // combine the row-splits and send with consecutive threads on consecutive units (coalesced)
+            __syncthreads();
+#pragma unroll
+            for (int q0 = 0; q0 < (ELS * PS + NT - 1) / NT; ++q0) {
+                const int i = tid + q0 * NT;
+                if ((ELS * PS) % NT != 0 && i >= ELS * PS) break;
+                const int k = i % ELS, p = i / ELS;
+                float v = 0.0f;
+#pragma unroll
+                for (int q = 0; q < RSPLIT; ++q) v += redb[(size_t)(q * PS + p) * ELS + k];
+                send(k, p, v);
+            }
+            if constexpr (CL) cluster_arrive();
         }
+        // item boundary: nobody may overwrite a buffer (or leave the kernel) while a peer still reads it
+        if constexpr (CL) { cluster_arrive(); cluster_wait(); }
         if (dead) break;
     }
 }
@@ -502,26 +599,101 @@ int num_sms() {
     return g_num_sms;
 }
 
-template <int ELS, int JB, int PS>
-int launch(bool backward, PersistArgs &a, cudaStream_t st, int *items_per_slot) {
+template <int ELS, int JB, int PS, bool CL>
+int prepare_kernel(bool backward, void (**kern)(PersistArgs), size_t *smem) {
     typedef Geo<ELS, JB, PS> Gm;
-    void (*kern)(PersistArgs) = backward ? lstm_bwd_persistent_kernel<ELS, JB, PS> : lstm_fwd_persistent_kernel<ELS, JB, PS>;
+    *kern = backward ? lstm_bwd_persistent_kernel<ELS, JB, PS, CL> : lstm_fwd_persistent_kernel<ELS, JB, PS, CL>;
+    *smem = backward ? Gm::bwd_smem(CL) : Gm::fwd_smem(CL);
+    static bool done[2] = {false, false};   // one flag per instantiation and direction
+    if (!done[backward ? 1 : 0]) {
+        B2_CUDA(cudaFuncSetAttribute(*kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)*smem));
+        done[backward ? 1 : 0] = true;
+    }
+    return B2_OK;
+}
+
+inline void cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, int G, int blocks, size_t smem, cudaStream_t st) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = G;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    *cfg = cudaLaunchConfig_t{};
+    cfg->gridDim = dim3(blocks);
+    cfg->blockDim = dim3(NT);
+    cfg->dynamicSmemBytes = smem;
+    cfg->stream = st;
+    cfg->attrs = attr;
+    cfg->numAttrs = 1;
+}
+
+// groups of at most 8 blocks run as thread-block clusters (distributed shared memory exchange)
+template <int ELS, int JB, int PS>
+int launch_cluster(bool backward, PersistArgs &a, cudaStream_t st, int *items_per_slot) {
+    typedef Geo<ELS, JB, PS> Gm;
+    if constexpr (Gm::G > 8) {
+        return 1;
+    } else {
+        void (*kern)(PersistArgs);
+        size_t smem;
+        B2_TRY((prepare_kernel<ELS, JB, PS, true>(backward, &kern, &smem)));
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[1];
+        cluster_config(&cfg, attr, Gm::G, Gm::G, smem, st);
+        int max_clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters < 1) {
+            cudaGetLastError();
+            return 1;   // no room for a cluster of this size: the caller uses the L2 exchange
+        }
+        int nslots = max_clusters < a.n_items ? max_clusters : a.n_items;
+        *items_per_slot = (a.n_items + nslots - 1) / nslots;
+        cfg.gridDim = dim3(nslots * Gm::G);
+        B2_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
+        count_launch();
+        return B2_OK;
+    }
+}
+
+template <int ELS, int JB, int PS>
+int launch(bool backward, bool use_cluster, PersistArgs &a, cudaStream_t st, int *items_per_slot) {
+    typedef Geo<ELS, JB, PS> Gm;
+    if (use_cluster) {
+        int rc = launch_cluster<ELS, JB, PS>(backward, a, st, items_per_slot);
+        if (rc != 1) return rc;
+    }
+    void (*kern)(PersistArgs);
+    size_t smem;
+    B2_TRY((prepare_kernel<ELS, JB, PS, false>(backward, &kern, &smem)));
     int per_sm = 0;
-    B2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, 0));
+    B2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, smem));
     int resident = per_sm * num_sms();
     int nslots = resident / Gm::G;
     if (nslots < 1) return 1;   // the group does not fit on the device together: caller falls back
     if (nslots > a.n_items) nslots = a.n_items;
     *items_per_slot = (a.n_items + nslots - 1) / nslots;
     void *args[] = {&a};
-    B2_CUDA(cudaLaunchCooperativeKernel((const void *)kern, dim3(nslots * Gm::G), dim3(NT), args, 0, st));
+    B2_CUDA(cudaLaunchCooperativeKernel((const void *)kern, dim3(nslots * Gm::G), dim3(NT), args, smem, st));
     count_launch();
     return B2_OK;
 }
 
+// how many clusters of G blocks of the (forward, 4 sequences) kernel the device can hold at once
+template <int ELS, int JB>
+int query_cluster_slots() {
+    typedef Geo<ELS, JB, 4> Gm;
+    void (*kern)(PersistArgs);
+    size_t smem;
+    if (prepare_kernel<ELS, JB, 4, true>(false, &kern, &smem) != B2_OK) return 0;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    cluster_config(&cfg, attr, Gm::G, Gm::G, smem, nullptr);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    return n;
+}
+
 }  // namespace
 
-// blocks per group and exchange words per slot for the geometry chosen for (els, PS)
+// hidden units per block for the register-resident geometry of `els` units per direction
 bool persistent_geometry(int els, int *JB) {
     switch (els) {
         case 1024: *JB = 8; return true;
@@ -532,15 +704,28 @@ bool persistent_geometry(int els, int *JB) {
     }
 }
 
+// 0 when groups of this size do not run as clusters
+int persistent_cluster_slots(int els) {
+    static int s256 = -1, s128 = -1;
+    if (els == 256) { if (s256 < 0) s256 = query_cluster_slots<256, 32>(); return s256; }
+    if (els == 128) { if (s128 < 0) s128 = query_cluster_slots<128, 64>(); return s128; }
+    return 0;
+}
+
 // Sequences per work item.  More sequences per item amortise the per-step exchange latency over more
 // work; fewer items than group slots leave SMs idle.  Take the smallest PS that lets every item have a
 // slot of its own, else the largest the register budget of the geometry allows.
-int persistent_ps(int els, int P, int D) {
+int persistent_ps(int els, int P, int D, bool use_cluster) {
     int JB;
     if (!persistent_geometry(els, &JB)) return 0;
     if (P == 1) return 1;
+    if (const char *e = getenv("B2_PS")) {   // experiments only: force the sequences per work item
+        int v = atoi(e);
+        if (v == 4 || v == 8 || (v == 16 && els < 1024)) return v;
+    }
     const int G = els / JB;
     int slots = num_sms() / G;
+    if (use_cluster && persistent_cluster_slots(els) > 0) slots = persistent_cluster_slots(els);
     if (slots < 1) slots = 1;
     const int max_ps = els >= 1024 ? 8 : 16;
     for (int ps = 4; ps <= max_ps; ps *= 2)
@@ -551,7 +736,9 @@ int persistent_ps(int els, int P, int D) {
 size_t lstm_persistent_xchg_words(int els, int P, int D) {
     int JB;
     if (!persistent_geometry(els, &JB)) return 0;
-    const int PS = persistent_ps(els, P, D), G = els / JB;
+    int PS = persistent_ps(els, P, D, false);
+    if (persistent_ps(els, P, D, true) > PS) PS = persistent_ps(els, P, D, true);
+    const int G = els / JB;
     int max_slots = num_sms() / G;
     if (max_slots < 1) max_slots = 1;
     size_t fwd = (size_t)4 * els * PS, bwd = (size_t)4 * G * G * JB * PS;
@@ -559,18 +746,18 @@ size_t lstm_persistent_xchg_words(int els, int P, int D) {
 }
 
 // returns B2_OK, an error, or 1 when this shape has no persistent kernel (caller uses the stepwise one)
-int lstm_persistent(bool backward, const LstmShape &s, const LstmBuffers &b, const float *w, float *y, const float *dy,
-                    unsigned long long *xchg, int *status, unsigned *tag_next, cudaStream_t st) {
+int lstm_persistent(bool backward, bool use_cluster, const LstmShape &s, const LstmBuffers &b, const float *w, float *y,
+                    const float *dy, unsigned long long *xchg, int *status, unsigned *tag_next, cudaStream_t st) {
     int JB;
     if (!persistent_geometry(s.els, &JB) || !xchg) return 1;
     PersistArgs a;
     a.sh = s; a.bf = b; a.w = w; a.y = y; a.dy = dy; a.xchg = xchg; a.status = status;
     a.tag_base = *tag_next;
-    const int PS = persistent_ps(s.els, s.P, s.D);
+    const int PS = persistent_ps(s.els, s.P, s.D, use_cluster);
     a.n_items = s.D * ((s.P + PS - 1) / PS);
     int ips = 1, rc = 1;
 #define CASE_PS(E, J, Q) \
-    case Q: rc = launch<E, J, Q>(backward, a, st, &ips); break;
+    case Q: rc = launch<E, J, Q>(backward, use_cluster, a, st, &ips); break;
 #define CASE(E, J, WITH16)                                       \
     case E:                                                      \
         switch (PS) {                                            \

@@ -12,8 +12,9 @@ from oracle import ref_available
 
 pytestmark = pytest.mark.gpu
 
-VARIANTS = [dict(recurrence=0, ffma=1), dict(recurrence=1, ffma=1), dict(recurrence=1, ffma=0), dict(recurrence=0, ffma=0)]
-VARIANT_IDS = ["stepwise-ffma", "persistent-ffma", "persistent-tensor", "stepwise-tensor"]
+VARIANTS = [dict(recurrence=0, ffma=1), dict(recurrence=1, ffma=1), dict(recurrence=1, ffma=0), dict(recurrence=2, ffma=0),
+            dict(recurrence=0, ffma=0)]
+VARIANT_IDS = ["stepwise-ffma", "persistent-ffma", "persistent-tensor", "persistent_cluster-tensor", "stepwise-tensor"]
 
 
 def run_gpu(layers, P, lens, x, tg, weights, variant, lr=1e-4, mom=0.9, maxT=None):
@@ -73,7 +74,7 @@ for els in (1, 3, 32, 33):
                 SHAPES.append((els, P, T, bi))
 
 
-@pytest.mark.parametrize("variant", VARIANTS[:3], ids=VARIANT_IDS[:3])
+@pytest.mark.parametrize("variant", VARIANTS[:4], ids=VARIANT_IDS[:4])
 def test_small_shapes_exhaustive(variant):
     """els in {1,3,32,33} x P in {1,3} x T in {1,2,5} x uni/bi, ragged lengths, run twice (determinism)."""
     from b2lstm import workloads
@@ -92,7 +93,7 @@ def test_small_shapes_exhaustive(variant):
                 assert np.array_equal(np.asarray(got[key]), np.asarray(again[key])), "not deterministic: " + key
 
 
-@pytest.mark.parametrize("variant", VARIANTS[:3], ids=VARIANT_IDS[:3])
+@pytest.mark.parametrize("variant", VARIANTS[:4], ids=VARIANT_IDS[:4])
 def test_cfg0_full(variant):
     """Configuration 0 at full size: 64 -> lstm 128 -> ff 32 -> sse, 4 x 200 frames."""
     from b2lstm import workloads
@@ -102,7 +103,7 @@ def test_cfg0_full(variant):
     parity.compare_run(wl["layers"], got, want, "cfg0")
 
 
-@pytest.mark.parametrize("variant", VARIANTS[1:3], ids=VARIANT_IDS[1:3])
+@pytest.mark.parametrize("variant", VARIANTS[1:4], ids=VARIANT_IDS[1:4])
 @pytest.mark.parametrize("cfg,P,scale", [(1, 6, 0.04), (3, 1, 0.01), (4, 5, 0.03)])
 def test_config_layer_sizes_reduced_frames(cfg, P, scale, variant):
     """Configurations 1, 3, 4 with their real layer sizes on a reduced frame budget (the checker is
@@ -114,7 +115,7 @@ def test_config_layer_sizes_reduced_frames(cfg, P, scale, variant):
     parity.compare_run(wl["layers"], got, want, "cfg%d reduced" % cfg, lstm_pad_zero_lens=wl["lens"])
 
 
-@pytest.mark.parametrize("variant", VARIANTS[1:3], ids=VARIANT_IDS[1:3])
+@pytest.mark.parametrize("variant", VARIANTS[1:4], ids=VARIANT_IDS[1:4])
 @pytest.mark.parametrize("ls,bi,P,lens", [(2048, 1, 5, [12, 12, 7, 3, 12]), (1024, 0, 1, [9]), (256, 1, 9, [14] * 9),
                                           (512, 1, 2, [6, 11]), (256, 0, 7, [10, 9, 8, 7, 6, 5, 4]),
                                           (512, 1, 40, [7] * 20 + [5] * 19 + [2]), (512, 1, 83, [5] * 80 + [3, 2, 1]),
