@@ -171,6 +171,17 @@ int b2_net_update_weights(b2_net *net, float learning_rate, float momentum);
  * hybrid_online_batch: load, forward, error, backward, [all-reduce], update.  *error may be NULL. */
 int b2_net_train_step(b2_net *net, int T, int n_seqs, const int *seq_lens, const float *host_inputs,
                       const float *host_targets, float learning_rate, float momentum, double *error);
+/* Overlap of the host -> device copy with compute (the role of the reference's optional loader
+ * thread, data_sets/DataSet.cpp:456-489): b2_net_prefetch_fraction starts copying the NEXT fraction
+ * (pinned host buffers, which must stay valid until the step that uses them has been enqueued) into
+ * the idle half of a double buffer on a copy stream and returns at once;
+ * b2_net_train_step_prefetched runs the train step on the fraction prefetched last. */
+int b2_net_prefetch_fraction(b2_net *net, int T, int n_seqs, const int *seq_lens, const float *host_inputs,
+                             const float *host_targets);
+int b2_net_train_step_prefetched(b2_net *net, float learning_rate, float momentum, double *error);
+/* Reads the error of the last forward pass back to the host; waits for the compute stream only (a
+ * prefetch in flight keeps running). */
+int b2_net_read_error(b2_net *net, double *error);
 /* Device-resident variant of the step above (no host<->device traffic, no synchronisation). */
 int b2_net_train_step_dev(b2_net *net, int T, int n_seqs, const int *seq_lens, const float *dev_inputs,
                           const float *dev_targets, float learning_rate, float momentum);

@@ -61,6 +61,9 @@ SIGNATURES = {
     "b2_net_update_weights": (C.c_int, [C.c_void_p, C.c_float, C.c_float]),
     "b2_net_train_step": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float,
                                     C.c_float, C.POINTER(C.c_double)]),
+    "b2_net_prefetch_fraction": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b2_net_train_step_prefetched": (C.c_int, [C.c_void_p, C.c_float, C.c_float, C.POINTER(C.c_double)]),
+    "b2_net_read_error": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
     "b2_net_train_step_dev": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float,
                                         C.c_float]),
     "b2_net_get_outputs": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
@@ -258,6 +261,24 @@ class Net:
         _check(lib().b2_net_train_step(self.h, inputs.shape[0], len(lens), lens.ctypes.data, inputs.ctypes.data,
                                        targets.ctypes.data, lr, momentum, C.byref(e) if want_error else None))
         return e.value if want_error else None
+
+    def prefetch_fraction(self, lens, inputs, targets):
+        """Start the host->device copy of the NEXT fraction (pinned host arrays that stay alive)."""
+        lens = np.ascontiguousarray(lens, np.int32)
+        self._next_T = int(lens.max())
+        _check(lib().b2_net_prefetch_fraction(self.h, inputs.shape[0], len(lens), lens.ctypes.data, inputs.ctypes.data,
+                                              targets.ctypes.data))
+
+    def train_step_prefetched(self, lr, momentum, want_error=True):
+        e = C.c_double()
+        _check(lib().b2_net_train_step_prefetched(self.h, lr, momentum, C.byref(e) if want_error else None))
+        self.T = self._next_T
+        return e.value if want_error else None
+
+    def read_error(self):
+        e = C.c_double()
+        _check(lib().b2_net_read_error(self.h, C.byref(e)))
+        return e.value
 
     def train_step_dev(self, lens, T, inputs_dev, targets_dev, lr, momentum):
         lens = self._lens(lens)

@@ -196,7 +196,15 @@ int SsePostOutputLayer::computeBackwardPass(int) {
 NeuralNetwork::~NeuralNetwork() {
     if (dp) dp_detach(*this);
     layers.clear();
-    cudaFree(ws); cudaFree(inDev); cudaFree(tgDev); cudaFree(patDev); cudaFree(statusDev);
+    cudaFree(ws); cudaFree(statusDev);
+    for (int b = 0; b < 2; ++b) {
+        cudaFree(inBuf[b]); cudaFree(tgBuf[b]); cudaFree(patBuf[b]);
+        if (patPinned[b]) cudaFreeHost(patPinned[b]);
+        if (prefetchDone[b]) cudaEventDestroy(prefetchDone[b]);
+        if (bufFree[b]) cudaEventDestroy(bufFree[b]);
+        if (patCopied[b]) cudaEventDestroy(patCopied[b]);
+    }
+    if (copyStream) cudaStreamDestroy(copyStream);
     tcScratch.release();
     for (size_t i = 0; i < eventPool.size(); ++i) cudaEventDestroy(eventPool[i]);
     for (size_t i = 0; i < prof.size(); ++i) { cudaEventDestroy(prof[i].a); cudaEventDestroy(prof[i].b); }
@@ -273,10 +281,16 @@ int NeuralNetwork::create(const char *networkJson, int P_, int maxT_, unsigned s
     }
     // fraction buffers (input layer outputs / targets / pattern types)
     size_t frames = (size_t)maxT * P;
-    B2_CUDA(cudaMalloc(&inDev, frames * layers.front()->size() * sizeof(float)));
-    B2_CUDA(cudaMalloc(&tgDev, frames * layers.back()->size() * sizeof(float)));
-    B2_CUDA(cudaMalloc(&patDev, frames));
-    patHost.assign(frames, 0);
+    B2_CUDA(cudaStreamCreateWithFlags(&copyStream, cudaStreamNonBlocking));
+    for (int b = 0; b < 2; ++b) {
+        B2_CUDA(cudaMalloc(&inBuf[b], frames * layers.front()->size() * sizeof(float)));
+        B2_CUDA(cudaMalloc(&tgBuf[b], frames * layers.back()->size() * sizeof(float)));
+        B2_CUDA(cudaMalloc(&patBuf[b], frames));
+        B2_CUDA(cudaMallocHost(&patPinned[b], frames));
+        B2_CUDA(cudaEventCreateWithFlags(&prefetchDone[b], cudaEventDisableTiming));
+        B2_CUDA(cudaEventCreateWithFlags(&bufFree[b], cudaEventDisableTiming));
+        B2_CUDA(cudaEventCreateWithFlags(&patCopied[b], cudaEventDisableTiming));
+    }
     wsFloats = (size_t)8 << 20;
     B2_CUDA(cudaMalloc(&ws, wsFloats * sizeof(float)));
     gradReady.resize(layers.size());
@@ -311,7 +325,9 @@ int NeuralNetwork::create(const char *networkJson, int P_, int maxT_, unsigned s
     return B2_OK;
 }
 
-int NeuralNetwork::loadFraction(int T, int nSeq, const int *lens, const float *in, const float *tg, bool onDevice) {
+// copies one fraction into buffer set b on stream st and fills fracBuf[b]
+int NeuralNetwork::stageFraction(int b, int T, int nSeq, const int *lens, const float *in, const float *tg, bool onDevice,
+                                 cudaStream_t st) {
     if (T <= 0 || T > maxT || nSeq <= 0 || nSeq > P || !lens || !in || !tg) {
         set_error("b2_net_load_fraction: T=%d (max %d), n_seqs=%d (P=%d)", T, maxT, nSeq, P);
         return B2_ERR_BAD_SHAPE;
@@ -326,16 +342,55 @@ int NeuralNetwork::loadFraction(int T, int nSeq, const int *lens, const float *i
     }
     // pattern types as DataSet::_makeFractionTask writes them (data_sets/DataSet.cpp:853-861)
     size_t frames = (size_t)mx * P;
-    memset(patHost.data(), 0, frames);
+    char *ph = patPinned[b];
+    // the pinned staging is rewritten by the host: the previous copy out of it must have run
+    B2_CUDA(cudaEventSynchronize(patCopied[b]));
+    memset(ph, 0, frames);
     for (int p = 0; p < nSeq; ++p)
-        for (int t = 0; t < lens[p]; ++t) patHost[(size_t)t * P + p] = t == 0 ? 1 : (t == lens[p] - 1 ? 3 : 2);
-    ProfScope ps(*this, "load_fraction");
-    B2_CUDA(cudaMemcpyAsync(patDev, patHost.data(), frames, cudaMemcpyHostToDevice, stream));
+        for (int t = 0; t < lens[p]; ++t) ph[(size_t)t * P + p] = t == 0 ? 1 : (t == lens[p] - 1 ? 3 : 2);
+    B2_CUDA(cudaMemcpyAsync(patBuf[b], ph, frames, cudaMemcpyHostToDevice, st));
+    B2_CUDA(cudaEventRecord(patCopied[b], st));
     cudaMemcpyKind kind = onDevice ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
-    B2_CUDA(cudaMemcpyAsync(inDev, in, frames * layers.front()->size() * sizeof(float), kind, stream));
-    B2_CUDA(cudaMemcpyAsync(tgDev, tg, frames * layers.back()->size() * sizeof(float), kind, stream));
-    frac.T = mx; frac.Tmin = mn; frac.nSeq = nSeq; frac.realFrames = real;
-    frac.patTypes = patDev; frac.inputs = inDev; frac.targets = tgDev;
+    B2_CUDA(cudaMemcpyAsync(inBuf[b], in, frames * layers.front()->size() * sizeof(float), kind, st));
+    B2_CUDA(cudaMemcpyAsync(tgBuf[b], tg, frames * layers.back()->size() * sizeof(float), kind, st));
+    Fraction &f = fracBuf[b];
+    f.T = mx; f.Tmin = mn; f.nSeq = nSeq; f.realFrames = real;
+    f.patTypes = patBuf[b]; f.inputs = inBuf[b]; f.targets = tgBuf[b];
+    return B2_OK;
+}
+
+int NeuralNetwork::loadFraction(int T, int nSeq, const int *lens, const float *in, const float *tg, bool onDevice) {
+    ProfScope ps(*this, "load_fraction");
+    if (prefetchPending) { set_error("b2_net_load_fraction: a prefetched fraction is waiting to be used"); return B2_ERR_STATE; }
+    B2_CUDA(cudaEventSynchronize(bufFree[cur]));
+    B2_TRY(stageFraction(cur, T, nSeq, lens, in, tg, onDevice, stream));
+    frac = fracBuf[cur];
+    for (size_t i = 0; i < layers.size(); ++i) B2_TRY(layers[i]->loadSequences(frac, 0));
+    return B2_OK;
+}
+
+// Start copying the NEXT fraction into the idle buffer set while the current one is being processed
+// (the role of the reference's optional loader thread, data_sets/DataSet.cpp:456-489,1936-1972).
+int NeuralNetwork::prefetchFraction(int T, int nSeq, const int *lens, const float *in, const float *tg) {
+    if (prefetchPending) { set_error("b2_net_prefetch_fraction: the previous prefetch has not been used yet"); return B2_ERR_STATE; }
+    const int b = cur ^ 1;
+    // the idle set was last read by the step before the current one; the host staging by its copy
+    B2_CUDA(cudaEventSynchronize(prefetchDone[b]));
+    B2_CUDA(cudaStreamWaitEvent(copyStream, bufFree[b], 0));
+    B2_TRY(stageFraction(b, T, nSeq, lens, in, tg, false, copyStream));
+    B2_CUDA(cudaEventRecord(prefetchDone[b], copyStream));
+    prefetchPending = true;
+    return B2_OK;
+}
+
+int NeuralNetwork::usePrefetched() {
+    if (!prefetchPending) { set_error("no prefetched fraction: call b2_net_prefetch_fraction first"); return B2_ERR_STATE; }
+    const int b = cur ^ 1;
+    B2_CUDA(cudaEventRecord(bufFree[cur], stream));            // everything enqueued so far has read the old set
+    B2_CUDA(cudaStreamWaitEvent(stream, prefetchDone[b], 0));
+    cur = b;
+    prefetchPending = false;
+    frac = fracBuf[cur];
     for (size_t i = 0; i < layers.size(); ++i) B2_TRY(layers[i]->loadSequences(frac, 0));
     return B2_OK;
 }
@@ -380,6 +435,7 @@ int NeuralNetwork::updateWeights(float lr, float mom) {
     return B2_OK;
 }
 int NeuralNetwork::synchronize() {
+    B2_CUDA(cudaStreamSynchronize(copyStream));
     B2_CUDA(cudaStreamSynchronize(stream));
     B2_CUDA(cudaStreamSynchronize(commStream));
     for (size_t i = 0; i < layers.size(); ++i) {
@@ -506,7 +562,7 @@ float *b2_net_weights_dev(b2_net *n, int i) { TrainableLayer *t = trainable(n, i
 float *b2_net_weight_updates_dev(b2_net *n, int i) { TrainableLayer *t = trainable(n, i); return t ? t->weightUpdates() : nullptr; }
 float *b2_net_outputs_dev(b2_net *n, int i) {
     if (!n || i < 0 || i >= (int)n->net.layers.size()) return nullptr;
-    return i == 0 ? n->net.inDev : n->net.layers[i]->outputs();
+    return i == 0 ? const_cast<float *>(n->net.frac.inputs) : n->net.layers[i]->outputs();
 }
 float *b2_net_output_errors_dev(b2_net *n, int i) {
     if (!n || i < 0 || i >= (int)n->net.layers.size()) return nullptr;
@@ -544,6 +600,32 @@ int b2_net_train_step(b2_net *n, int T, int nSeq, const int *lens, const float *
     }
     return B2_OK;
 }
+int b2_net_prefetch_fraction(b2_net *n, int T, int nSeq, const int *lens, const float *in, const float *tg) {
+    if (!n) return B2_ERR_BAD_ARG;
+    return n->net.prefetchFraction(T, nSeq, lens, in, tg);
+}
+int b2_net_train_step_prefetched(b2_net *n, float lr, float mom, double *error) {
+    if (!n) return B2_ERR_BAD_ARG;
+    B2_TRY(n->net.usePrefetched());
+    B2_TRY(n->net.computeForwardPass());
+    B2_TRY(n->net.calculateError(nullptr));
+    B2_TRY(n->net.computeBackwardPass());
+    B2_TRY(n->net.updateWeights(lr, mom));
+    if (error) {
+        SsePostOutputLayer *post = dynamic_cast<SsePostOutputLayer *>(n->net.layers.back().get());
+        B2_CUDA(cudaMemcpyAsync(error, post->lossDev(), sizeof(double), cudaMemcpyDeviceToHost, n->net.stream));
+        B2_CUDA(cudaStreamSynchronize(n->net.stream));
+    }
+    return B2_OK;
+}
+int b2_net_read_error(b2_net *n, double *error) {
+    if (!n || !error) return B2_ERR_BAD_ARG;
+    SsePostOutputLayer *post = dynamic_cast<SsePostOutputLayer *>(n->net.layers.back().get());
+    if (!post) { set_error("the last layer is not a post-output layer"); return B2_ERR_STATE; }
+    B2_CUDA(cudaMemcpyAsync(error, post->lossDev(), sizeof(double), cudaMemcpyDeviceToHost, n->net.stream));
+    B2_CUDA(cudaStreamSynchronize(n->net.stream));
+    return B2_OK;
+}
 int b2_net_train_step_dev(b2_net *n, int T, int nSeq, const int *lens, const float *in, const float *tg, float lr,
                           float mom) {
     if (!n) return B2_ERR_BAD_ARG;
@@ -557,8 +639,8 @@ int b2_net_train_step_dev(b2_net *n, int T, int nSeq, const int *lens, const flo
 static int copy_layer_vec(b2_net *n, int i, float *host, bool errors) {
     if (!n || !host || i < 0 || i >= (int)n->net.layers.size()) { set_error("bad layer index %d", i); return B2_ERR_BAD_ARG; }
     Layer *l = n->net.layers[i].get();
-    const float *src = errors ? l->outputErrors() : (i == 0 ? n->net.inDev : l->outputs());
-    if (dynamic_cast<SsePostOutputLayer *>(l)) src = errors ? nullptr : n->net.tgDev;
+    const float *src = errors ? l->outputErrors() : (i == 0 ? n->net.frac.inputs : l->outputs());
+    if (dynamic_cast<SsePostOutputLayer *>(l)) src = errors ? nullptr : n->net.frac.targets;
     if (!src) { set_error("layer %d keeps no such vector", i); return B2_ERR_BAD_ARG; }
     B2_TRY(n->net.synchronize());
     B2_CUDA(cudaMemcpy(host, src, (size_t)n->net.frac.T * n->net.P * l->size() * sizeof(float), cudaMemcpyDeviceToHost));

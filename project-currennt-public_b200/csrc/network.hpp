@@ -157,10 +157,20 @@ public:
     // tensor-core GEMMs: arena for the tf32 hi/lo operand copies, device status word of their waits
     TcScratch tcScratch;
     int *statusDev = nullptr;
-    // device copies of the current fraction
-    float *inDev = nullptr, *tgDev = nullptr;
-    char *patDev = nullptr;
-    std::vector<char> patHost;
+    // device copies of the current fraction, double-buffered so that the next fraction can be copied
+    // (on copyStream) while the current one is being processed
+    float *inBuf[2] = {nullptr, nullptr}, *tgBuf[2] = {nullptr, nullptr};
+    char *patBuf[2] = {nullptr, nullptr};
+    char *patPinned[2] = {nullptr, nullptr};   // pinned host staging of the pattern types
+    Fraction fracBuf[2];
+    int cur = 0;
+    bool prefetchPending = false;
+    cudaStream_t copyStream = nullptr;
+    cudaEvent_t prefetchDone[2] = {nullptr, nullptr}, bufFree[2] = {nullptr, nullptr}, patCopied[2] = {nullptr, nullptr};
+    int stageFraction(int b, int T, int nSeq, const int *lens, const float *in, const float *tg, bool onDevice,
+                      cudaStream_t st);
+    int prefetchFraction(int T, int nSeq, const int *lens, const float *in, const float *tg);
+    int usePrefetched();
     // profiling
     bool profiling = false;
     std::vector<ProfileEntry> prof;

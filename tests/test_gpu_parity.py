@@ -158,6 +158,46 @@ def test_reuse_across_fractions_of_different_length():
     net.close()
 
 
+def test_prefetched_steps_equal_plain_steps():
+    """Three train steps on three different fractions: once with b2_net_train_step (copy, then
+    compute), once with the copy of the next fraction prefetched under the current step.  Same
+    errors and bit-identical weights."""
+    import torch
+    import b2lstm
+    from b2lstm import workloads
+    layers = L(("input", 12), ("blstm", 256), ("feedforward_identity", 5), ("sse", 5))
+    P = 6
+    w = workloads.make_weights(layers, 61, 0.1)
+    fracs = []
+    for k, lens in enumerate([[20, 20, 11, 9, 4, 2], [13] * 6, [25, 3, 3]]):
+        lens = np.array(lens, np.int32)
+        x, tg = workloads.make_fraction(12, 5, P, lens, 70 + k, 80 + k)
+        fracs.append((lens, torch.from_numpy(x).pin_memory(), torch.from_numpy(tg).pin_memory()))
+    results = []
+    for mode in ("plain", "prefetched"):
+        net = b2lstm.Net(layers, P, 25)
+        for i, wi in w.items():
+            net.set_weights(i, wi)
+        errs = []
+        if mode == "plain":
+            for lens, x, tg in fracs:
+                errs.append(net.train_step(lens, x.numpy(), tg.numpy(), 1e-3, 0.9))
+        else:
+            net.prefetch_fraction(fracs[0][0], fracs[0][1].numpy(), fracs[0][2].numpy())
+            for k in range(len(fracs)):
+                net.train_step_prefetched(1e-3, 0.9, want_error=False)
+                if k + 1 < len(fracs):
+                    net.prefetch_fraction(fracs[k + 1][0], fracs[k + 1][1].numpy(), fracs[k + 1][2].numpy())
+                errs.append(net.read_error())
+        net.synchronize()
+        results.append((errs, {i: net.get_weights(i) for i in w}))
+        net.close()
+    assert results[0][0] == results[1][0]
+    for i in w:
+        assert np.array_equal(results[0][1][i], results[1][1][i])
+        assert not np.array_equal(results[0][1][i], w[i])
+
+
 def test_layer_level_entry_points_on_caller_buffers():
     """b2_lstm_* on torch-owned device buffers, the drop-in for layers::LstmLayer<Gpu>."""
     import torch
