@@ -109,7 +109,9 @@ int b2_lstm_backward(b2_lstm *layer, const float *weights_dev, const float *x_de
 /* Which recurrence kernels run: 0 = one launch per timestep; 1 = persistent kernel exchanging
  * through L2 (default; measured fastest on B200); 2 = persistent kernel exchanging through
  * distributed shared memory where a group fits a thread-block cluster (128 or 256 units per
- * direction), through L2 otherwise. */
+ * direction), through L2 otherwise; 3 = tensor-core recurrence (one batched tcgen05 GEMM and one
+ * gate kernel per timestep) wherever the shape allows it.  In mode 1 the library itself switches to
+ * the tensor-core recurrence for large batches (many sequences x many units), where it is faster. */
 int b2_lstm_set_recurrence_mode(b2_lstm *layer, int mode);
 /* Waits for the work enqueued on `stream` and reports what the layer's kernels recorded:
  * B2_ERR_STEP_TIMEOUT if a persistent kernel gave up a bounded wait, else B2_OK. */

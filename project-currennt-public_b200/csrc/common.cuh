@@ -77,6 +77,16 @@ int split_operand(TcScratch &sc, const float *src, long s_outer, int outer, int 
 bool gemm_tc_supported(const SplitOperand &A, const SplitOperand &B, int m, int n, int k);
 int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, int m, int n, int k, bool accumulate,
             float *ws, size_t ws_floats, int *status, cudaStream_t st);
+// Planned, batched launches of the tensor-core kernel: tensor maps encoded once, many launches that
+// differ in coordinate offsets.  Batch b shifts operand A by (a_in, a_out) and B by (b_in, b_out) in
+// (contiguous index, other index) coordinates and writes split z to C + c_off + z*c_split_stride.
+struct TcBatch { int a_in, a_out, b_in, b_out; long long c_off; };
+struct TcPlan;
+int tc_plan_create(TcPlan **out, const SplitOperand &A, long a_inner, long a_outer, const SplitOperand &B, long b_inner,
+                   long b_outer, int m, int n, int k, int splits, int kseg_len, int kseg_stride, long ldc);
+int tc_plan_launch(const TcPlan *p, float *C, const TcBatch *batches, int nbatch, long long c_split_stride, int *status,
+                   cudaStream_t st);
+void tc_plan_destroy(TcPlan *p);
 bool gemm_wants_tc(long sam, long sak, long sbk, long sbn, int m, int n, int k);
 // picks the tensor-core kernel when the shape qualifies (and sc/status are given), else FFMA
 int gemm_auto(float *C, long ldc, const float *A, long sam, long sak, const float *B, long sbk, long sbn, int m, int n,
@@ -124,8 +134,25 @@ int lstm_prepare_wrecT(const LstmShape &s, const float *w, float *wrecT, cudaStr
 int lstm_vector_grads(const LstmShape &s, const LstmBuffers &b, float *dw, float *ws, size_t ws_floats,
                       cudaStream_t st);
 
+// tensor-core recurrence for large batches (lstm_step_tc.cu): one batched tcgen05 GEMM + one gate
+// kernel per timestep.  The buffers hold the tf32 hi/lo parts of the recurrent weights, of the block
+// outputs and of the gate deltas, and the K-split partial sums of one step.
+struct TcRecBuffers {
+    float *wrec_hi = nullptr, *wrec_lo = nullptr;   // [4*ls][els]
+    float *y_hi = nullptr, *y_lo = nullptr;         // [T*P][ls]
+    float *d_hi = nullptr, *d_lo = nullptr;         // [T*P][4*ls]
+    float *part = nullptr;
+};
+bool lstm_tc_supported(const LstmShape &s);
+size_t lstm_tc_part_floats(int P, int els, int D);
+int lstm_forward_tc(const LstmShape &s, const LstmBuffers &bf, const TcRecBuffers &rb, const float *w, float *y, int *status,
+                    cudaStream_t st);
+int lstm_backward_tc(const LstmShape &s, const LstmBuffers &bf, const TcRecBuffers &rb, const float *w, const float *dy,
+                     int *status, cudaStream_t st);
+
 // persistent kernels (lstm_persistent.cu).  Return B2_OK, an error, or 1 when the shape has no
 // persistent kernel (the caller then uses the stepwise kernels).
+bool persistent_geometry(int els, int *JB);   // hidden units per block of the register-resident geometry
 size_t lstm_persistent_xchg_words(int els, int P, int D);
 int persistent_ps(int els, int P, int D, bool use_cluster);   // sequences per work item for a shape (0: no persistent kernel)
 // use_cluster: groups of <= 8 blocks exchange through distributed shared memory (thread-block clusters)

@@ -34,6 +34,7 @@ constexpr int TILE_BYTES = BM * BK * 4;                 // 16 KiB: one operand p
 constexpr int STAGE_BYTES = 4 * TILE_BYTES;             // A_hi, A_lo, B_hi, B_lo
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024; // + slack to align the ring to 1024 B
 constexpr int NTHREADS = 192;
+constexpr int TC_MAX_BATCH = 8;
 constexpr int SEG = 2;                                  // slabs per drained accumulator segment
 constexpr int TMEM_COLS = 512;                          // 2 x 128 main accumulator + 128 cross terms (power of two)
 constexpr long long WAIT_CYCLES = 4000000000LL;         // about two seconds
@@ -121,6 +122,17 @@ struct TcArgs {
     int accumulate;
     float *ws;         // split-K partials [z][N][M] when gridDim.z > 1
     int *status;
+    // Batched use (nbatch > 0): blockIdx.z = batch * splits + split.  A batch shifts the tensor-map
+    // coordinates of both operands and the output pointer; split z of batch b writes (never
+    // accumulates) to C + c_off[b] + z * c_split_stride with leading dimension ldc.
+    int nbatch, splits;
+    int a_off_inner[TC_MAX_BATCH], a_off_outer[TC_MAX_BATCH];
+    int b_off_inner[TC_MAX_BATCH], b_off_outer[TC_MAX_BATCH];
+    long long c_off[TC_MAX_BATCH];
+    long long c_split_stride;
+    // The contraction index may run over segments of kseg_len consecutive positions that lie
+    // kseg_stride apart in both operands (the four gate blocks of one direction); 0 = contiguous.
+    int kseg_len, kseg_stride;
 };
 
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -141,7 +153,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
     auto big_empty = [&](int b) { return bar0 + 8u * (uint32_t)(2 * STAGES + 2 + b); };
 
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-    const int kbeg = blockIdx.z * a.kchunk;
+    const int zsplit = a.nbatch ? (int)blockIdx.z % a.splits : (int)blockIdx.z;
+    const int batch = a.nbatch ? (int)blockIdx.z / a.splits : 0;
+    const int a_in = a.nbatch ? a.a_off_inner[batch] : 0, a_out = a.nbatch ? a.a_off_outer[batch] : 0;
+    const int b_in = a.nbatch ? a.b_off_inner[batch] : 0, b_out = a.nbatch ? a.b_off_outer[batch] : 0;
+    const int kbeg = zsplit * a.kchunk;
     const int kend = min(a.K, kbeg + a.kchunk);
     const int nkb = (kend - kbeg + BK - 1) / BK;
 
@@ -170,26 +186,28 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
                 const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
                 if (!mbar_wait(empty_bar(s), ph ^ 1u)) { fail_s = 1; break; }
                 const uint32_t base = ring + (uint32_t)s * STAGE_BYTES;
-                const int k0 = kbeg + kb * BK;
+                int k0 = kbeg + kb * BK;
+                if (a.kseg_len) k0 = (k0 / a.kseg_len) * a.kseg_stride + k0 % a.kseg_len;   // segmented contraction index
                 mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                // the contraction index is the inner coordinate of a K-major operand, the outer one otherwise
                 if (a.a_kmajor) {
-                    tma_load_2d(base, &mapAhi, k0, m0, full_bar(s));
-                    tma_load_2d(base + TILE_BYTES, &mapAlo, k0, m0, full_bar(s));
+                    tma_load_2d(base, &mapAhi, k0 + a_in, m0 + a_out, full_bar(s));
+                    tma_load_2d(base + TILE_BYTES, &mapAlo, k0 + a_in, m0 + a_out, full_bar(s));
                 } else {
 #pragma unroll
                     for (int b = 0; b < BM / 32; ++b) {
-                        tma_load_2d(base + b * 4096, &mapAhi, m0 + 32 * b, k0, full_bar(s));
-                        tma_load_2d(base + TILE_BYTES + b * 4096, &mapAlo, m0 + 32 * b, k0, full_bar(s));
+                        tma_load_2d(base + b * 4096, &mapAhi, m0 + 32 * b + a_in, k0 + a_out, full_bar(s));
+                        tma_load_2d(base + TILE_BYTES + b * 4096, &mapAlo, m0 + 32 * b + a_in, k0 + a_out, full_bar(s));
                     }
                 }
                 if (a.b_kmajor) {
-                    tma_load_2d(base + 2 * TILE_BYTES, &mapBhi, k0, n0, full_bar(s));
-                    tma_load_2d(base + 3 * TILE_BYTES, &mapBlo, k0, n0, full_bar(s));
+                    tma_load_2d(base + 2 * TILE_BYTES, &mapBhi, k0 + b_in, n0 + b_out, full_bar(s));
+                    tma_load_2d(base + 3 * TILE_BYTES, &mapBlo, k0 + b_in, n0 + b_out, full_bar(s));
                 } else {
 #pragma unroll
                     for (int b = 0; b < BN / 32; ++b) {
-                        tma_load_2d(base + 2 * TILE_BYTES + b * 4096, &mapBhi, n0 + 32 * b, k0, full_bar(s));
-                        tma_load_2d(base + 3 * TILE_BYTES + b * 4096, &mapBlo, n0 + 32 * b, k0, full_bar(s));
+                        tma_load_2d(base + 2 * TILE_BYTES + b * 4096, &mapBhi, n0 + 32 * b + b_in, k0 + b_out, full_bar(s));
+                        tma_load_2d(base + 3 * TILE_BYTES + b * 4096, &mapBlo, n0 + 32 * b + b_in, k0 + b_out, full_bar(s));
                     }
                 }
             }
@@ -272,8 +290,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
             if (lane == 0) fail_s = 1;
         } else {
             const int m = m0 + 32 * q + lane;
-            const bool split = gridDim.z > 1;
-            float *dst = split ? a.ws + (size_t)blockIdx.z * (size_t)a.M * a.N : a.C;
+            const bool batched = a.nbatch > 0;
+            const bool split = !batched && gridDim.z > 1;
+            float *dst = batched ? a.C + a.c_off[batch] + (long long)zsplit * a.c_split_stride
+                                 : (split ? a.ws + (size_t)blockIdx.z * (size_t)a.M * a.N : a.C);
             const long ld = split ? (long)a.M : a.ldc;
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -287,7 +307,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
                         if (n < a.N) {
                             float *p = dst + (size_t)n * ld + m;
                             float v = acc[c0 + j] + __uint_as_float(r[j]);
-                            if (!split && a.accumulate) v += *p;
+                            if (!split && !batched && a.accumulate) v += *p;
                             *p = v;
                         }
                     }
@@ -437,6 +457,7 @@ int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, in
     a.C = C; a.ldc = ldc; a.M = m; a.N = n; a.K = k; a.kchunk = kchunk;
     a.a_kmajor = A.kmajor ? 1 : 0; a.b_kmajor = B.kmajor ? 1 : 0;
     a.accumulate = accumulate ? 1 : 0; a.ws = ws; a.status = status;
+    a.nbatch = 0; a.splits = splits; a.c_split_stride = 0; a.kseg_len = 0; a.kseg_stride = 0;
     gemm_tf32x3_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(mAh, mAl, mBh, mBl, a);
     count_launch();
     B2_CUDA(cudaGetLastError());
@@ -448,6 +469,61 @@ int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, in
         count_launch();
         B2_CUDA(cudaGetLastError());
     }
+    return B2_OK;
+}
+
+// ---- planned, batched launches: the tensor maps are encoded once and reused for many launches that
+// differ only in coordinate offsets (one launch per timestep of the tensor-core recurrence)
+struct TcPlan {
+    CUtensorMap mAh, mAl, mBh, mBl;
+    TcArgs args;
+    dim3 grid;
+};
+
+int tc_plan_create(TcPlan **out, const SplitOperand &A, long a_inner, long a_outer, const SplitOperand &B, long b_inner,
+                   long b_outer, int m, int n, int k, int splits, int kseg_len, int kseg_stride, long ldc) {
+    B2_TRY(get_encode());
+    if (!g_attr_set) {
+        B2_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        g_attr_set = true;
+    }
+    if (splits < 1 || (k % (splits * BK)) != 0 || (kseg_len && (kseg_len % BK) != 0)) {
+        set_error("tc_plan_create: k=%d must divide into %d splits of whole %d-slabs (segment %d)", k, splits, BK, kseg_len);
+        return B2_ERR_BAD_SHAPE;
+    }
+    TcPlan *p = new TcPlan;
+    int rc = make_map(&p->mAh, A.hi, a_inner, a_outer, A.ld, A.kmajor ? BK : 32, A.kmajor ? BM : BK, A.kmajor);
+    if (rc == B2_OK) rc = make_map(&p->mAl, A.lo, a_inner, a_outer, A.ld, A.kmajor ? BK : 32, A.kmajor ? BM : BK, A.kmajor);
+    if (rc == B2_OK) rc = make_map(&p->mBh, B.hi, b_inner, b_outer, B.ld, B.kmajor ? BK : 32, B.kmajor ? BN : BK, B.kmajor);
+    if (rc == B2_OK) rc = make_map(&p->mBl, B.lo, b_inner, b_outer, B.ld, B.kmajor ? BK : 32, B.kmajor ? BN : BK, B.kmajor);
+    if (rc != B2_OK) { delete p; return rc; }
+    TcArgs &a = p->args;
+    a = TcArgs{};
+    a.ldc = ldc; a.M = m; a.N = n; a.K = k; a.kchunk = k / splits;
+    a.a_kmajor = A.kmajor ? 1 : 0; a.b_kmajor = B.kmajor ? 1 : 0;
+    a.splits = splits; a.kseg_len = kseg_len; a.kseg_stride = kseg_stride;
+    p->grid = dim3((m + BM - 1) / BM, (n + BN - 1) / BN, 1);
+    *out = p;
+    return B2_OK;
+}
+
+void tc_plan_destroy(TcPlan *p) { delete p; }
+
+int tc_plan_launch(const TcPlan *p, float *C, const TcBatch *batches, int nbatch, long long c_split_stride, int *status,
+                   cudaStream_t st) {
+    if (nbatch < 1 || nbatch > TC_MAX_BATCH) { set_error("tc_plan_launch: 1..%d batches", TC_MAX_BATCH); return B2_ERR_BAD_ARG; }
+    TcArgs a = p->args;
+    a.C = C; a.status = status; a.nbatch = nbatch; a.c_split_stride = c_split_stride;
+    for (int b = 0; b < nbatch; ++b) {
+        a.a_off_inner[b] = batches[b].a_in; a.a_off_outer[b] = batches[b].a_out;
+        a.b_off_inner[b] = batches[b].b_in; a.b_off_outer[b] = batches[b].b_out;
+        a.c_off[b] = batches[b].c_off;
+    }
+    dim3 grid = p->grid;
+    grid.z = nbatch * a.splits;
+    gemm_tf32x3_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(p->mAh, p->mAl, p->mBh, p->mBl, a);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
     return B2_OK;
 }
 

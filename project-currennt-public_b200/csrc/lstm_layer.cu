@@ -66,6 +66,9 @@ int LstmLayerImpl::create(const b2_lstm_desc &d) {
 void LstmLayerImpl::destroy() {
     cudaFree(bufs.acts); cudaFree(bufs.cells); cudaFree(bufs.deltas); cudaFree(bufs.cerr); cudaFree(bufs.wrecT);
     cudaFree(ws); cudaFree(xchg); cudaFree(status_dev);
+    cudaFree(tcrec.wrec_hi); cudaFree(tcrec.wrec_lo); cudaFree(tcrec.y_hi); cudaFree(tcrec.y_lo);
+    cudaFree(tcrec.d_hi); cudaFree(tcrec.d_lo); cudaFree(tcrec.part);
+    tcrec = TcRecBuffers();
     if (own_scratch) { own_scratch->release(); delete own_scratch; own_scratch = nullptr; scratch = nullptr; }
     bufs = LstmBuffers();
     ws = nullptr; xchg = nullptr; status_dev = nullptr;
@@ -102,7 +105,14 @@ int LstmLayerImpl::forward(const float *w, const float *x, float *y, cudaStream_
     {
         Phase ph(*this, "lstm_fwd_recurrence");
         B2_TRY(lstm_prepare_wrecT(s, w, bufs.wrecT, st));
-        int rc = recurrence_mode >= 1 ? lstm_persistent(false, recurrence_mode == 2, s, bufs, w, y, nullptr, xchg, status_dev, &tag_next, st) : 1;
+        int rc = 1;
+        tcrec_used = want_tc_recurrence();
+        if (tcrec_used) {
+            B2_TRY(ensure_tcrec());
+            rc = lstm_forward_tc(s, bufs, tcrec, w, y, status_dev, st);
+        } else if (recurrence_mode >= 1) {
+            rc = lstm_persistent(false, recurrence_mode == 2, s, bufs, w, y, nullptr, xchg, status_dev, &tag_next, st);
+        }
         if (rc == 1) rc = lstm_forward_stepwise(s, bufs, w, y, st);
         B2_TRY(rc);
     }
@@ -119,7 +129,10 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
     const LstmOffsets off = lstm_offsets(pls, ls, els);
     {
         Phase ph(*this, "lstm_bwd_recurrence");
-        int rc = recurrence_mode >= 1 ? lstm_persistent(true, recurrence_mode == 2, s, bufs, w, nullptr, dy, xchg, status_dev, &tag_next, st) : 1;
+        int rc = 1;
+        if (tcrec_used) rc = lstm_backward_tc(s, bufs, tcrec, w, dy, status_dev, st);
+        else if (recurrence_mode >= 1)
+            rc = lstm_persistent(true, recurrence_mode == 2, s, bufs, w, nullptr, dy, xchg, status_dev, &tag_next, st);
         if (rc == 1) rc = lstm_backward_stepwise(s, bufs, w, dy, st);
         B2_TRY(rc);
     }
@@ -134,9 +147,15 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
         B2_TRY(scratch->reserve(split_floats(N, 4 * ls) + split_floats(N, pls) + split_floats(N, ls) +
                                 split_floats(4 * ls, pls)));
         scratch->used = 0;
-        B2_TRY(split_operand(*scratch, bufs.deltas, 4 * ls, N, 4 * ls, true, &sD, st));
+        if (tcrec_used) {
+            // the tensor-core recurrence has already written the hi/lo parts of the deltas and of y
+            sD.hi = tcrec.d_hi; sD.lo = tcrec.d_lo; sD.ld = 4 * ls; sD.kmajor = true;
+            sY.hi = tcrec.y_hi; sY.lo = tcrec.y_lo; sY.ld = ls; sY.kmajor = false;
+        } else {
+            B2_TRY(split_operand(*scratch, bufs.deltas, 4 * ls, N, 4 * ls, true, &sD, st));
+            B2_TRY(split_operand(*scratch, y, ls, N, ls, false, &sY, st));
+        }
         B2_TRY(split_operand(*scratch, x, pls, N, pls, false, &sX, st));
-        B2_TRY(split_operand(*scratch, y, ls, N, ls, false, &sY, st));
         B2_TRY(split_operand(*scratch, w, pls, 4 * ls, pls, false, &sW, st));
     }
     // error to the preceding layer (reference: 4*D Sgemm, LstmLayer.cu:2298-2334): dX = W_in * deltas
@@ -186,6 +205,40 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
     }
     Phase ph(*this, "lstm_vector_grads");
     B2_TRY(lstm_vector_grads(s, bufs, dw, ws, ws_floats, st));
+    return B2_OK;
+}
+
+// Which recurrence runs.  Mode 3 forces the tensor-core recurrence where the shape allows it; the
+// default (mode 1) picks it when the persistent kernel would need many passes of expensive steps:
+// measured on B200 a persistent step costs about 1.4 us + 0.27 us per sequence of a work item, a
+// tensor-core step (GEMM + gate kernel, two launches) about 10 us whatever the batch.
+bool LstmLayerImpl::want_tc_recurrence() const {
+    const LstmShape s = shape();
+    if (force_ffma || !lstm_tc_supported(s) || (desc.size % 4) != 0) return false;
+    if (recurrence_mode == 3) return true;
+    if (recurrence_mode != 1 || s.P < 16) return false;
+    const int ps = persistent_ps(s.els, s.P, s.D, false);
+    if (ps == 0) return s.els >= 256;
+    int JB = 0;
+    persistent_geometry(s.els, &JB);
+    int slots = 148 / (s.els / JB);
+    if (slots < 1) slots = 1;
+    const int items = s.D * ((s.P + ps - 1) / ps);
+    const int passes = (items + slots - 1) / slots;
+    return passes * (1.4 + 0.27 * ps) > 12.0;
+}
+
+int LstmLayerImpl::ensure_tcrec() {
+    if (tcrec.y_hi) return B2_OK;
+    const size_t frames = (size_t)desc.max_seq_length * desc.parallel_sequences, ls = desc.size;
+    B2_CUDA(cudaMalloc(&tcrec.wrec_hi, (size_t)4 * ls * els * sizeof(float)));
+    B2_CUDA(cudaMalloc(&tcrec.wrec_lo, (size_t)4 * ls * els * sizeof(float)));
+    B2_CUDA(cudaMalloc(&tcrec.y_hi, frames * ls * sizeof(float)));
+    B2_CUDA(cudaMalloc(&tcrec.y_lo, frames * ls * sizeof(float)));
+    B2_CUDA(cudaMalloc(&tcrec.d_hi, frames * 4 * ls * sizeof(float)));
+    B2_CUDA(cudaMalloc(&tcrec.d_lo, frames * 4 * ls * sizeof(float)));
+    B2_CUDA(cudaMalloc(&tcrec.part, lstm_tc_part_floats(desc.parallel_sequences, els, D) * sizeof(float)));
+    state_bytes += (frames * 10 * ls + (size_t)8 * ls * els + lstm_tc_part_floats(desc.parallel_sequences, els, D)) * sizeof(float);
     return B2_OK;
 }
 

@@ -22,6 +22,11 @@ struct LstmLayerImpl {
     unsigned long long *xchg = nullptr;
     int *status_dev = nullptr;
     unsigned tag_next = 1;
+    // tensor-core recurrence (large batches): hi/lo buffers, allocated on first use
+    TcRecBuffers tcrec{};
+    bool tcrec_used = false;      // this fraction's forward sweep ran on the tensor-core recurrence
+    bool want_tc_recurrence() const;
+    int ensure_tcrec();
     int check_status(cudaStream_t st);   // synchronises st; returns the kernels' status word
     // optional per-phase timing hooks (set by the layer stack when profiling is on)
     void *prof_ctx = nullptr;

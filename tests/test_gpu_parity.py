@@ -13,8 +13,9 @@ from oracle import ref_available
 pytestmark = pytest.mark.gpu
 
 VARIANTS = [dict(recurrence=0, ffma=1), dict(recurrence=1, ffma=1), dict(recurrence=1, ffma=0), dict(recurrence=2, ffma=0),
-            dict(recurrence=0, ffma=0)]
-VARIANT_IDS = ["stepwise-ffma", "persistent-ffma", "persistent-tensor", "persistent_cluster-tensor", "stepwise-tensor"]
+            dict(recurrence=3, ffma=0), dict(recurrence=0, ffma=0)]
+VARIANT_IDS = ["stepwise-ffma", "persistent-ffma", "persistent-tensor", "persistent_cluster-tensor", "tensor_recurrence-tensor",
+               "stepwise-tensor"]
 
 
 def run_gpu(layers, P, lens, x, tg, weights, variant, lr=1e-4, mom=0.9, maxT=None):
@@ -93,7 +94,7 @@ def test_small_shapes_exhaustive(variant):
                 assert np.array_equal(np.asarray(got[key]), np.asarray(again[key])), "not deterministic: " + key
 
 
-@pytest.mark.parametrize("variant", VARIANTS[:4], ids=VARIANT_IDS[:4])
+@pytest.mark.parametrize("variant", VARIANTS[:5], ids=VARIANT_IDS[:5])
 def test_cfg0_full(variant):
     """Configuration 0 at full size: 64 -> lstm 128 -> ff 32 -> sse, 4 x 200 frames."""
     from b2lstm import workloads
@@ -103,7 +104,7 @@ def test_cfg0_full(variant):
     parity.compare_run(wl["layers"], got, want, "cfg0")
 
 
-@pytest.mark.parametrize("variant", VARIANTS[1:4], ids=VARIANT_IDS[1:4])
+@pytest.mark.parametrize("variant", VARIANTS[1:5], ids=VARIANT_IDS[1:5])
 @pytest.mark.parametrize("cfg,P,scale", [(1, 6, 0.04), (3, 1, 0.01), (4, 5, 0.03)])
 def test_config_layer_sizes_reduced_frames(cfg, P, scale, variant):
     """Configurations 1, 3, 4 with their real layer sizes on a reduced frame budget (the checker is
@@ -115,7 +116,7 @@ def test_config_layer_sizes_reduced_frames(cfg, P, scale, variant):
     parity.compare_run(wl["layers"], got, want, "cfg%d reduced" % cfg, lstm_pad_zero_lens=wl["lens"])
 
 
-@pytest.mark.parametrize("variant", VARIANTS[1:4], ids=VARIANT_IDS[1:4])
+@pytest.mark.parametrize("variant", VARIANTS[1:5], ids=VARIANT_IDS[1:5])
 @pytest.mark.parametrize("ls,bi,P,lens", [(2048, 1, 5, [12, 12, 7, 3, 12]), (1024, 0, 1, [9]), (256, 1, 9, [14] * 9),
                                           (512, 1, 2, [6, 11]), (256, 0, 7, [10, 9, 8, 7, 6, 5, 4]),
                                           (512, 1, 40, [7] * 20 + [5] * 19 + [2]), (512, 1, 83, [5] * 80 + [3, 2, 1]),
