@@ -221,6 +221,64 @@ int b2_dp_detach(b2_net *net);
 /* Sum a double over all ranks (loss / frame counts). Synchronises. */
 int b2_dp_allreduce_scalar(b2_net *net, double *value);
 
+/* ------------------------------------------------------------------------------------------
+ * Data sets: the toolkit's .nc files (netCDF classic; CURRENNT_codes/README section 5) read
+ * into fractions of parallel_sequences sequences.  Host code; replaces data_sets::DataSet
+ * (data_sets/DataSet.hpp:47-369) and DataSetFraction (data_sets/DataSetFraction.hpp:40-263)
+ * for regression data.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct b2_data b2_data;
+
+typedef struct {
+    int parallel_sequences;   /* --parallel_sequences */
+    float fraction;           /* --train_fraction and the like: portion of each file's sequences, (0, 1] */
+    int trunc_seq_length;     /* --truncate_seq: > 0 cuts sequences into segments (DataSet.cpp:1465-1500) */
+    int fraction_shuffling;   /* --shuffle_fractions */
+    int sequence_shuffling;   /* --shuffle_sequences */
+    unsigned random_seed;     /* --random_seed: seeds the process-wide shuffle generator at its first use */
+    int training_mode;        /* non-zero: segments are sorted by length (DataSet.cpp:1898-1900) */
+    int loader_threads;       /* threads that convert one fraction; 0 = min(8, hardware threads) */
+} b2_data_options;
+
+typedef struct {
+    int max_seq_length;       /* DataSetFraction::maxSeqLength: T of this fraction */
+    int min_seq_length;
+    int num_sequences;        /* <= parallel_sequences (the last fraction of an epoch may be short) */
+    long long total_frames;   /* DataSetFraction::fracTimeLength: real frames */
+    const int *seq_lengths;   /* [num_sequences] */
+    const float *inputs;      /* [max_seq_length * parallel_sequences * input_size], index (t*P + p)*size + d */
+    const float *targets;     /* [max_seq_length * parallel_sequences * output_size] */
+    const char *pat_types;    /* [max_seq_length * parallel_sequences]: 0 none, 1 first, 2 normal, 3 last */
+} b2_fraction;
+
+/* DataSet::DataSet(ncfiles, parSeq, fraction, truncSeqLength, fracShuf, seqShuf, ...)
+ * (DataSet.cpp:1303-1907).  Errors (B2_ERR_BAD_ARG) carry the reference's messages. */
+int b2_data_open(b2_data **out, const char *const *nc_paths, int n_files, const b2_data_options *opt);
+void b2_data_close(b2_data *data);
+/* totalSequences, totalTimesteps, minSeqLength, maxSeqLength, inputPatternSize, outputPatternSize */
+int b2_data_info(const b2_data *data, int *total_sequences, long long *total_timesteps, int *min_seq_length,
+                 int *max_seq_length, int *input_size, int *output_size);
+/* outputMeans / outputStdevs of the first file; *present = 0 (and 0 / 1 values) when the file has none */
+int b2_data_output_mean_stdev(const b2_data *data, float *means, float *stdevs, int *present);
+/* DataSet::getNextFraction (DataSet.cpp:1943-1995): returns B2_OK and fills *frac, or
+ * B2_DATA_EPOCH_END once after the last fraction of an epoch (the reference returns a null
+ * pointer there).  The buffers behind *frac are pinned when a GPU is present and stay valid for
+ * the next two calls; the following fraction is assembled by a loader thread meanwhile. */
+#define B2_DATA_EPOCH_END 1
+int b2_data_next_fraction(b2_data *data, b2_fraction *frac);
+/* seq_info_t of sequence i of the fraction returned last: utterance name, index of the segment in
+ * its utterance. */
+int b2_data_fraction_seq_info(const b2_data *data, int i, char *tag, int tag_capacity, int *original_seq_idx);
+/* Re-seeds the process-wide generator that sequence and fraction shuffling draw from. */
+void b2_data_reseed(unsigned seed);
+/* One pass of Optimizer::_processDataSet over a data set with weight updates after every fraction
+ * (hybrid_online_batch; optimizers/Optimizer.cu:68-231): the next fraction is copied to the device
+ * while the current one trains.  *error = sum over fractions of (fraction error / totalSequences)
+ * as the reference accumulates it; with learning_rate < 0 nothing is updated (validation pass:
+ * forward and error only). */
+int b2_net_train_epoch(b2_net *net, b2_data *data, float learning_rate, float momentum, double *error,
+                       long long *frames);
+
 #ifdef __cplusplus
 }
 #endif

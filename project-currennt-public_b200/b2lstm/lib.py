@@ -79,6 +79,15 @@ SIGNATURES = {
     "b2_dp_attach": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "b2_dp_detach": (C.c_int, [C.c_void_p]),
     "b2_dp_allreduce_scalar": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
+    "b2_data_open": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_char_p), C.c_int, C.c_void_p]),
+    "b2_data_close": (None, [C.c_void_p]),
+    "b2_data_info": (C.c_int, [C.c_void_p, _ip, C.POINTER(C.c_longlong), _ip, _ip, _ip, _ip]),
+    "b2_data_output_mean_stdev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, _ip]),
+    "b2_data_next_fraction": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b2_data_fraction_seq_info": (C.c_int, [C.c_void_p, C.c_int, C.c_char_p, C.c_int, _ip]),
+    "b2_data_reseed": (None, [C.c_uint]),
+    "b2_net_train_epoch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.POINTER(C.c_double),
+                                     C.POINTER(C.c_longlong)]),
 }
 
 _lib = None
@@ -335,3 +344,128 @@ class Net:
         d = C.c_double(v)
         _check(lib().b2_dp_allreduce_scalar(self.h, C.byref(d)))
         return d.value
+
+
+class _DataOptions(C.Structure):
+    _fields_ = [("parallel_sequences", C.c_int), ("fraction", C.c_float), ("trunc_seq_length", C.c_int),
+                ("fraction_shuffling", C.c_int), ("sequence_shuffling", C.c_int), ("random_seed", C.c_uint),
+                ("training_mode", C.c_int), ("loader_threads", C.c_int)]
+
+
+class _Fraction(C.Structure):
+    _fields_ = [("max_seq_length", C.c_int), ("min_seq_length", C.c_int), ("num_sequences", C.c_int),
+                ("total_frames", C.c_longlong), ("seq_lengths", _ip), ("inputs", _fp), ("targets", _fp),
+                ("pat_types", C.POINTER(C.c_char))]
+
+
+class DataSet:
+    """data_sets::DataSet of the reference over .nc files (b2_data_*): iterate epochs with
+    `for frac in ds.epoch():`; a fraction is a dict of numpy views that stay valid for two more
+    fractions."""
+
+    def __init__(self, paths, parallel_sequences, fraction=1.0, trunc_seq_length=0, fraction_shuffling=False,
+                 sequence_shuffling=False, random_seed=0, training_mode=True, loader_threads=0):
+        if isinstance(paths, str):
+            paths = [paths]
+        arr = (C.c_char_p * len(paths))(*[os.fsencode(p) for p in paths])
+        opt = _DataOptions(parallel_sequences, fraction, trunc_seq_length, int(fraction_shuffling),
+                           int(sequence_shuffling), random_seed, int(training_mode), loader_threads)
+        self.h = C.c_void_p()
+        _check(lib().b2_data_open(C.byref(self.h), arr, len(paths), C.byref(opt)))
+        self.P = parallel_sequences
+        n, ts, mn, mx, i, o = C.c_int(), C.c_longlong(), C.c_int(), C.c_int(), C.c_int(), C.c_int()
+        _check(lib().b2_data_info(self.h, C.byref(n), C.byref(ts), C.byref(mn), C.byref(mx), C.byref(i), C.byref(o)))
+        self.total_sequences, self.total_timesteps = n.value, ts.value
+        self.min_seq_length, self.max_seq_length = mn.value, mx.value
+        self.input_size, self.output_size = i.value, o.value
+
+    def close(self):
+        if self.h:
+            lib().b2_data_close(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def output_mean_stdev(self):
+        m = np.zeros(self.output_size, np.float32)
+        s = np.zeros(self.output_size, np.float32)
+        present = C.c_int()
+        _check(lib().b2_data_output_mean_stdev(self.h, m.ctypes.data, s.ctypes.data, C.byref(present)))
+        return m, s, bool(present.value)
+
+    def next_fraction(self):
+        """dict for the next fraction, or None once at the end of an epoch"""
+        f = _Fraction()
+        rc = lib().b2_data_next_fraction(self.h, C.byref(f))
+        if rc == 1:
+            return None
+        _check(rc)
+        T, P, n = f.max_seq_length, self.P, f.num_sequences
+        tags, orig = [], []
+        buf = C.create_string_buffer(1024)
+        k = C.c_int()
+        for i in range(n):
+            _check(lib().b2_data_fraction_seq_info(self.h, i, buf, 1024, C.byref(k)))
+            tags.append(buf.value.decode())
+            orig.append(k.value)
+        return {"T": T, "min_seq_length": f.min_seq_length, "num_sequences": n, "total_frames": f.total_frames,
+                "seq_lengths": np.ctypeslib.as_array(f.seq_lengths, (n,)).copy(),
+                "inputs": np.ctypeslib.as_array(f.inputs, (T, P, self.input_size)),
+                "targets": np.ctypeslib.as_array(f.targets, (T, P, self.output_size)),
+                "pat_types": np.frombuffer(C.string_at(f.pat_types, T * P), np.int8).reshape(T, P),
+                "tags": tags, "original_seq_idx": orig}
+
+    def epoch(self):
+        while True:
+            f = self.next_fraction()
+            if f is None:
+                return
+            yield f
+
+
+def data_reseed(seed):
+    lib().b2_data_reseed(seed)
+
+
+def train_epoch(net, data, lr, momentum):
+    """b2_net_train_epoch: (error, frames); lr < 0 = validation pass (forward and error only)"""
+    e, n = C.c_double(), C.c_longlong()
+    _check(lib().b2_net_train_epoch(net.h, data.h, lr, momentum, C.byref(e), C.byref(n)))
+    return e.value, n.value
+
+
+def write_nc(path, seq_tags, seq_lengths, inputs, targets, output_means=None, output_stdevs=None, version=2):
+    """Writes a data set in the toolkit's .nc layout (netCDF classic via scipy, as the reference's
+    pyTools/dataTools/ncDataHandle.py does): inputs [numTimesteps, inputPattSize], targets
+    [numTimesteps, targetPattSize], sequences back to back."""
+    from scipy.io import netcdf_file
+    inputs = np.asarray(inputs, np.float32)
+    targets = np.asarray(targets, np.float32)
+    n = len(seq_lengths)
+    taglen = max(len(t) for t in seq_tags) + 1
+    with netcdf_file(path, "w", version=version) as f:
+        f.createDimension("numSeqs", n)
+        f.createDimension("numTimesteps", inputs.shape[0])
+        f.createDimension("inputPattSize", inputs.shape[1])
+        f.createDimension("targetPattSize", targets.shape[1])
+        f.createDimension("maxSeqTagLength", taglen)
+        tv = f.createVariable("seqTags", "S1", ("numSeqs", "maxSeqTagLength"))
+        lv = f.createVariable("seqLengths", "i", ("numSeqs",))
+        iv = f.createVariable("inputs", "f", ("numTimesteps", "inputPattSize"))
+        ov = f.createVariable("targetPatterns", "f", ("numTimesteps", "targetPattSize"))
+        tags = np.zeros((n, taglen), "S1")
+        for i, t in enumerate(seq_tags):
+            tags[i, :len(t)] = list(t)
+        tv[:] = tags
+        lv[:] = np.asarray(seq_lengths, np.int32)
+        iv[:] = inputs
+        ov[:] = targets
+        if output_means is not None:
+            mv = f.createVariable("outputMeans", "f", ("targetPattSize",))
+            sv = f.createVariable("outputStdevs", "f", ("targetPattSize",))
+            mv[:] = np.asarray(output_means, np.float32)
+            sv[:] = np.asarray(output_stdevs, np.float32)

@@ -112,3 +112,17 @@ def gemm_flops_per_frame(layers):
             els = ls // 2 if ty == "blstm" else ls
             f += 8 * ls * pls + 8 * ls * els
     return f
+
+
+def write_nc(wl, path):
+    """Writes a built workload as a data set in the toolkit's .nc layout (sequences back to back,
+    padding frames dropped); reading it with parallel_sequences = wl["P"] and training_mode off
+    gives back the same fraction."""
+    from .lib import write_nc as _write
+    P, lens = wl["P"], wl["lens"]
+    T = int(lens.max())
+    x = np.asarray(wl["x"]).reshape(T, P, -1)
+    tg = np.asarray(wl["tg"]).reshape(T, P, -1)
+    xs = np.concatenate([x[:int(n), p] for p, n in enumerate(lens)], axis=0)
+    ts = np.concatenate([tg[:int(n), p] for p, n in enumerate(lens)], axis=0)
+    _write(path, ["seq%05d" % p for p in range(P)], [int(n) for n in lens], xs, ts)
