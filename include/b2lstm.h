@@ -279,6 +279,59 @@ void b2_data_reseed(unsigned seed);
 int b2_net_train_epoch(b2_net *net, b2_data *data, float learning_rate, float momentum, double *error,
                        long long *frames);
 
+/* ------------------------------------------------------------------------------------------
+ * Network export, and the training run around the epoch loop: validation-based early
+ * stopping, best-weight bookkeeping, autosave / continue.  The JSON documents use the
+ * reference's member names, so files travel between the two implementations.
+ * ------------------------------------------------------------------------------------------ */
+/* NeuralNetwork::exportLayers + exportWeights (NeuralNetwork.cpp:2993-3043;
+ * layers/TrainableLayer.cu:441-480): {"layers":[{name,type,size,bias[,learningRate]}],
+ * "weights":{name:{"input":[..],"bias":[..],"internal":[..]}}} as text.  buf may be NULL to ask
+ * for the size (*needed, including the terminating NUL).  digits: significant digits of every
+ * number; <= 0 means 9 (exact for fp32); 6 is what the reference's writer prints ("%g"). */
+int b2_net_export_json(b2_net *net, char *buf, size_t capacity, size_t *needed, int digits);
+/* NeuralNetwork::saveNetwork (NeuralNetwork.cpp:4104-4125): the same document into a file
+ * (trained_network.jsn). */
+int b2_net_save_network(b2_net *net, const char *filename, int digits);
+/* The momentum term of SteepestDescentOptimizer (m_weightDeltas, SteepestDescentOptimizer.cu:421-438)
+ * of one layer, host <-> device; part of the autosave state. */
+int b2_net_get_weight_deltas(b2_net *net, int layer, float *host_out);
+int b2_net_set_weight_deltas(b2_net *net, int layer, const float *host_in);
+
+typedef struct b2_optimizer b2_optimizer;
+typedef struct {
+    float learning_rate;       /* --learning_rate */
+    float momentum;            /* --momentum */
+    int max_epochs;            /* --max_epochs; < 0: no limit */
+    int max_epochs_no_best;    /* --max_epochs_no_best */
+    int validate_every;        /* --validate_every */
+    int test_every;            /* --test_every */
+} b2_optimizer_options;
+typedef struct {
+    int finished, cur_epoch, epochs_since_lowest_error;
+    float lowest_validation_error;
+    float cur_training_error, cur_validation_error, cur_test_error;   /* sum over fractions of error / totalSequences */
+    float cur_training_error_per_frame, cur_validation_error_per_frame, cur_test_error_per_frame;
+} b2_optimizer_state;
+/* optimizers::SteepestDescentOptimizer(network, trainingSet, validationSet, testSet, maxEpochs,
+ * maxEpochsNoBest, validateEvery, testEvery, learningRate, momentum) (Optimizer.cu:375-421);
+ * validation_set and test_set may be NULL (the reference passes empty data sets). */
+int b2_optimizer_create(b2_optimizer **out, b2_net *net, b2_data *training_set, b2_data *validation_set,
+                        b2_data *test_set, const b2_optimizer_options *options);
+void b2_optimizer_destroy(b2_optimizer *opt);
+/* Optimizer::train (Optimizer.cu:565-689): one epoch over the training set with weight updates,
+ * then validation / test passes when due; stores the weights on a new lowest validation error,
+ * restores the best weights and sets *finished when max_epochs or max_epochs_no_best is reached. */
+int b2_optimizer_train(b2_optimizer *opt, int *finished);
+int b2_optimizer_get_state(const b2_optimizer *opt, b2_optimizer_state *state);
+/* Optimizer::saveState (Optimizer.cu:851-933, the "epochNNN.autosave" files): configuration and
+ * info rows as given, network, optimizer members, best weights and momentum deltas. */
+int b2_optimizer_save_state(b2_optimizer *opt, const char *filename, const char *configuration, const char *info_rows,
+                            int digits);
+/* --continue: weights from the file's "weights" section, then Optimizer::restoreState /
+ * importState (Optimizer.cu:728-765, 915-930).  info_rows may be NULL. */
+int b2_optimizer_restore_state(b2_optimizer *opt, const char *filename, char *info_rows, size_t info_capacity);
+
 #ifdef __cplusplus
 }
 #endif

@@ -88,6 +88,16 @@ SIGNATURES = {
     "b2_data_reseed": (None, [C.c_uint]),
     "b2_net_train_epoch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.POINTER(C.c_double),
                                      C.POINTER(C.c_longlong)]),
+    "b2_net_export_json": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t), C.c_int]),
+    "b2_net_save_network": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
+    "b2_net_get_weight_deltas": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "b2_net_set_weight_deltas": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "b2_optimizer_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b2_optimizer_destroy": (None, [C.c_void_p]),
+    "b2_optimizer_train": (C.c_int, [C.c_void_p, _ip]),
+    "b2_optimizer_get_state": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b2_optimizer_save_state": (C.c_int, [C.c_void_p, C.c_char_p, C.c_char_p, C.c_char_p, C.c_int]),
+    "b2_optimizer_restore_state": (C.c_int, [C.c_void_p, C.c_char_p, C.c_char_p, C.c_size_t]),
 }
 
 _lib = None
@@ -334,6 +344,26 @@ class Net:
         n = lib().b2_net_get_profile(self.h, cap, names, ms, ln)
         return {names[i].decode(): (float(ms[i]), int(ln[i])) for i in range(n)}
 
+    def export_json(self, digits=0):
+        """The network as the reference's network.jsn text (layers + weights)."""
+        need = C.c_size_t()
+        _check(lib().b2_net_export_json(self.h, None, 0, C.byref(need), digits))
+        buf = C.create_string_buffer(need.value)
+        _check(lib().b2_net_export_json(self.h, buf, need.value, None, digits))
+        return buf.value.decode()
+
+    def save_network(self, filename, digits=0):
+        _check(lib().b2_net_save_network(self.h, os.fsencode(filename), digits))
+
+    def weight_deltas(self, i):
+        out = np.empty(self.num_weights(i), np.float32)
+        _check(lib().b2_net_get_weight_deltas(self.h, i, out.ctypes.data))
+        return out
+
+    def set_weight_deltas(self, i, d):
+        d = np.ascontiguousarray(d, np.float32)
+        _check(lib().b2_net_set_weight_deltas(self.h, i, d.ctypes.data))
+
     def dp_attach(self, rank, world, unique_id):
         _check(lib().b2_dp_attach(self.h, rank, world, unique_id))
 
@@ -469,3 +499,60 @@ def write_nc(path, seq_tags, seq_lengths, inputs, targets, output_means=None, ou
             sv = f.createVariable("outputStdevs", "f", ("targetPattSize",))
             mv[:] = np.asarray(output_means, np.float32)
             sv[:] = np.asarray(output_stdevs, np.float32)
+
+
+class _OptimizerOptions(C.Structure):
+    _fields_ = [("learning_rate", C.c_float), ("momentum", C.c_float), ("max_epochs", C.c_int),
+                ("max_epochs_no_best", C.c_int), ("validate_every", C.c_int), ("test_every", C.c_int)]
+
+
+class _OptimizerState(C.Structure):
+    _fields_ = [("finished", C.c_int), ("cur_epoch", C.c_int), ("epochs_since_lowest_error", C.c_int),
+                ("lowest_validation_error", C.c_float), ("cur_training_error", C.c_float),
+                ("cur_validation_error", C.c_float), ("cur_test_error", C.c_float),
+                ("cur_training_error_per_frame", C.c_float), ("cur_validation_error_per_frame", C.c_float),
+                ("cur_test_error_per_frame", C.c_float)]
+
+
+class Optimizer:
+    """optimizers::SteepestDescentOptimizer of the reference around a Net and its data sets:
+    train() runs one epoch (plus validation / test passes when due) and returns True when finished."""
+
+    def __init__(self, net, training_set, validation_set=None, test_set=None, learning_rate=1e-5, momentum=0.9,
+                 max_epochs=-1, max_epochs_no_best=20, validate_every=1, test_every=1):
+        opt = _OptimizerOptions(learning_rate, momentum, max_epochs, max_epochs_no_best, validate_every, test_every)
+        self.h = C.c_void_p()
+        self._keep = (net, training_set, validation_set, test_set)
+        _check(lib().b2_optimizer_create(C.byref(self.h), net.h, training_set.h,
+                                         validation_set.h if validation_set else None,
+                                         test_set.h if test_set else None, C.byref(opt)))
+
+    def close(self):
+        if self.h:
+            lib().b2_optimizer_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def train(self):
+        fin = C.c_int()
+        _check(lib().b2_optimizer_train(self.h, C.byref(fin)))
+        return bool(fin.value)
+
+    @property
+    def state(self):
+        s = _OptimizerState()
+        _check(lib().b2_optimizer_get_state(self.h, C.byref(s)))
+        return {k: getattr(s, k) for k, _ in _OptimizerState._fields_}
+
+    def save_state(self, filename, configuration="", info_rows="", digits=0):
+        _check(lib().b2_optimizer_save_state(self.h, os.fsencode(filename), configuration.encode(), info_rows.encode(), digits))
+
+    def restore_state(self, filename):
+        buf = C.create_string_buffer(1 << 16)
+        _check(lib().b2_optimizer_restore_state(self.h, os.fsencode(filename), buf, len(buf)))
+        return buf.value.decode()

@@ -1,0 +1,126 @@
+"""GPU tests of network export and of the training run around the epoch loop (b2_net_export_json,
+b2_optimizer_*): JSON round trips with the reference's member names, early stopping on the
+validation error, autosave / continue."""
+import json
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def L(*spec):
+    return [dict(type=t, size=s, **({} if t in ("input", "sse") else {"bias": 1.0})) for t, s in spec]
+
+
+LAYERS = L(("input", 7), ("feedforward_tanh", 12), ("blstm", 16), ("lstm", 9), ("feedforward_identity", 3), ("sse", 3))
+
+
+def corpus(tmp_path, name, lens, seed, w_true):
+    """targets are a fixed linear map of the inputs plus noise: something a few epochs can learn"""
+    import b2lstm
+    rng = np.random.default_rng(seed)
+    n = int(sum(lens))
+    x = rng.standard_normal((n, 7)).astype(np.float32)
+    y = (np.tanh(x @ w_true) + 0.05 * rng.standard_normal((n, 3))).astype(np.float32)
+    path = str(tmp_path / name)
+    b2lstm.write_nc(path, ["%s%03d" % (name[:2], i) for i in range(len(lens))], lens, x, y)
+    return path
+
+
+def test_export_json_round_trips_exactly_and_keeps_the_reference_layout():
+    import b2lstm
+    from b2lstm import workloads
+    w = workloads.make_weights(LAYERS, 5, 0.3)
+    net = b2lstm.Net(LAYERS, 2, 8)
+    for i, wi in w.items():
+        net.set_weights(i, wi)
+    doc = json.loads(net.export_json())
+    assert [l["type"] for l in doc["layers"]] == [l["type"] for l in LAYERS]
+    assert [l["size"] for l in doc["layers"]] == [l["size"] for l in LAYERS]
+    assert all(("bias" in l) == (l["type"] not in ("input", "sse")) for l in doc["layers"])
+    for i, wi in w.items():
+        sec = doc["weights"][doc["layers"][i]["name"]]
+        ls, pls = LAYERS[i]["size"], LAYERS[i - 1]["size"]
+        per = 4 if "lstm" in LAYERS[i]["type"] else 1
+        assert len(sec["input"]) == ls * per * pls and len(sec["bias"]) == ls * per
+        flat = np.array(sec["input"] + sec["bias"] + sec["internal"], np.float32)
+        assert np.array_equal(flat, wi)                     # 9 significant digits: exact for fp32
+    # a net created from the exported document holds the same weights
+    net2 = b2lstm.Net([{k: v for k, v in l.items()} for l in doc["layers"]], 2, 8, weights=doc["weights"])
+    for i, wi in w.items():
+        assert np.array_equal(net2.get_weights(i), wi)
+    # the reference's writer prints "%g": six digits
+    short = json.loads(net.export_json(digits=6))
+    a = np.array(short["weights"][doc["layers"][2]["name"]]["input"], np.float32)
+    assert np.allclose(a, w[2][:a.size], rtol=1e-5) and not np.array_equal(a, w[2][:a.size])
+    net.close()
+    net2.close()
+
+
+def test_training_run_stops_on_validation_error_and_restores_best_weights(tmp_path):
+    import b2lstm
+    from b2lstm import workloads
+    w_true = np.random.default_rng(0).standard_normal((7, 3)).astype(np.float32)
+    train = corpus(tmp_path, "train.nc", [20, 35, 28, 31, 25, 22, 38, 27], 1, w_true)
+    valid = corpus(tmp_path, "valid.nc", [30, 24, 33], 2, w_true)
+    P = 4
+    w = workloads.make_weights(LAYERS, 9, 0.1)
+
+    def fresh():
+        net = b2lstm.Net(LAYERS, P, 40)
+        for i, wi in w.items():
+            net.set_weights(i, wi)
+        return net
+
+    net = fresh()
+    tr, va = b2lstm.DataSet(train, P), b2lstm.DataSet(valid, P)
+    opt = b2lstm.Optimizer(net, tr, va, learning_rate=3e-4, momentum=0.9, max_epochs=6, max_epochs_no_best=3)
+    hist = []
+    while not opt.train():
+        hist.append(opt.state)
+    hist.append(opt.state)
+    assert hist[-1]["finished"] == 1 and hist[-1]["cur_epoch"] == len(hist) <= 6
+    assert hist[-1]["cur_training_error"] < hist[0]["cur_training_error"]          # it learns
+    best = min(h["cur_validation_error"] for h in hist)
+    assert hist[-1]["lowest_validation_error"] == best
+    # finished: the weights of the best validation epoch are back in the net
+    e, _ = b2lstm.train_epoch(net, va, -1.0, 0.0)
+    assert abs(e - best) <= 1e-6 * abs(best)
+    per_frame = hist[-1]["cur_training_error"] * tr.total_sequences / tr.total_timesteps
+    assert abs(hist[-1]["cur_training_error_per_frame"] - per_frame) <= 1e-6 * per_frame
+
+    # autosave after two epochs, continue in a fresh process state: same trajectory as an uninterrupted run
+    net_a = fresh()
+    tr_a, va_a = b2lstm.DataSet(train, P), b2lstm.DataSet(valid, P)
+    opt_a = b2lstm.Optimizer(net_a, tr_a, va_a, learning_rate=3e-4, momentum=0.9, max_epochs=6, max_epochs_no_best=3)
+    opt_a.train()
+    opt_a.train()
+    save = str(tmp_path / "epoch002.autosave")
+    opt_a.save_state(save, configuration="max_epochs = 6", info_rows="row one\nrow two")
+    doc = json.load(open(save))
+    for key in ("configuration", "info_rows", "layers", "weights", "optimizer_finished", "optimizer_cur_epoch",
+                "optimizer_epochs_since_lowest_error", "optimizer_lowest_validation_error", "optimizer_cur_training_error",
+                "optimizer_cur_validation_error", "optimizer_cur_test_error", "optimizer_status", "optimizer_best_weights",
+                "steepest_descent_optimizer_weight_deltas"):
+        assert key in doc, key
+    assert doc["optimizer_cur_epoch"] == 2 and doc["info_rows"] == "row one;;;row two"
+    assert len(doc["optimizer_best_weights"]) == len(LAYERS) and doc["optimizer_best_weights"][0] == []
+
+    net_b = b2lstm.Net(LAYERS, P, 40, seed=999)                    # different initial weights on purpose
+    tr_b, va_b = b2lstm.DataSet(train, P), b2lstm.DataSet(valid, P)
+    opt_b = b2lstm.Optimizer(net_b, tr_b, va_b, learning_rate=3e-4, momentum=0.9, max_epochs=6, max_epochs_no_best=3)
+    assert opt_b.restore_state(save) == "row one\nrow two"
+    saved = lambda st: {k: v for k, v in st.items() if not k.endswith("_per_frame")}   # per-frame errors are not part of the file
+    assert saved(opt_b.state) == saved(opt_a.state)
+    for i in w:
+        assert np.array_equal(net_b.get_weights(i), net_a.get_weights(i))
+        assert np.array_equal(net_b.weight_deltas(i), net_a.weight_deltas(i))
+    fa, fb = opt_a.train(), opt_b.train()
+    assert fa == fb and opt_a.state == opt_b.state == hist[2]
+    for i in w:
+        assert np.array_equal(net_b.get_weights(i), net_a.get_weights(i))
+    for o in (opt, opt_a, opt_b):
+        o.close()
+    for n in (net, net_a, net_b):
+        n.close()
