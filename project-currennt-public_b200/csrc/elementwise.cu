@@ -57,13 +57,13 @@ __global__ void ff_delta_kernel(float *__restrict__ err, const float *__restrict
         err[i] = apply_deriv(act, y[i]) * err[i];
 }
 
-constexpr int CS_ROWS = 512;  // rows (frames) per partial sum
 __global__ void column_sums_partial_kernel(float *__restrict__ ws, const float *__restrict__ m, long ld, int cols,
-                                           long rows) {
+                                           long rows, int rows_per_chunk) {
     int u = blockIdx.x * blockDim.x + threadIdx.x;
     if (u >= cols) return;
-    long r0 = (long)blockIdx.y * CS_ROWS, r1 = min(rows, r0 + CS_ROWS);
+    long r0 = (long)blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
     float s = 0.0f;
+#pragma unroll 8
     for (long r = r0; r < r1; ++r) s += m[(size_t)r * ld + u];
     ws[(size_t)blockIdx.y * cols + u] = s;
 }
@@ -156,14 +156,18 @@ int ff_delta(float *err, const float *y, size_t n, int act, cudaStream_t st) {
 
 int column_sums(float *out, const float *m, long ld, int cols, long rows, float scale, float *ws, size_t ws_floats,
                 cudaStream_t st) {
-    int chunks = (int)((rows + CS_ROWS - 1) / CS_ROWS);
-    if (chunks < 1) chunks = 1;
-    if ((size_t)chunks * cols > ws_floats) {
+    // rows (frames) per partial sum: enough blocks to fill the device several times, bounded by the scratch
+    int rpc = 64;
+    const long max_chunks = cols > 0 ? (long)(ws_floats / (size_t)cols) : 0;
+    if (max_chunks < 1) {
         set_error("column_sums: scratch too small");
         return B2_ERR_BAD_SHAPE;
     }
+    if ((rows + rpc - 1) / rpc > max_chunks) rpc = (int)((rows + max_chunks - 1) / max_chunks);
+    int chunks = (int)((rows + rpc - 1) / rpc);
+    if (chunks < 1) chunks = 1;
     dim3 grid((cols + 127) / 128, chunks);
-    column_sums_partial_kernel<<<grid, 128, 0, st>>>(ws, m, ld, cols, rows);
+    column_sums_partial_kernel<<<grid, 128, 0, st>>>(ws, m, ld, cols, rows, rpc);
     column_sums_reduce_kernel<<<(cols + 127) / 128, 128, 0, st>>>(out, ws, cols, chunks, scale);
     count_launch(2);
     B2_CUDA(cudaGetLastError());

@@ -352,6 +352,46 @@ __global__ void split_tf32_kernel(const float *__restrict__ src, long s_outer, i
     }
 }
 
+// the same for rows that are whole float4 groups (inner, the source stride and all bases multiples of 4)
+__device__ __forceinline__ void split4(const float4 x, float4 &h, float4 &l) {
+    const float in[4] = {x.x, x.y, x.z, x.w};
+    float hh[4], ll[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t a, b;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(a) : "f"(in[i]));
+        const float rem = in[i] - __uint_as_float(a);
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(b) : "f"(rem));
+        hh[i] = __uint_as_float(a);
+        ll[i] = __uint_as_float(b);
+    }
+    h = make_float4(hh[0], hh[1], hh[2], hh[3]);
+    l = make_float4(ll[0], ll[1], ll[2], ll[3]);
+}
+__global__ void __launch_bounds__(256) split_tf32_vec4_kernel(const float *__restrict__ src, long s_outer, int outer, int inner4,
+                                                              float4 *__restrict__ hi, float4 *__restrict__ lo) {
+    const size_t total = (size_t)outer * inner4;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // two independent groups per iteration keep more loads in flight
+    for (; i + stride < total; i += 2 * stride) {
+        const size_t j = i + stride;
+        const float4 x0 = __ldg((const float4 *)(src + (i / inner4) * s_outer) + (i % inner4));
+        const float4 x1 = __ldg((const float4 *)(src + (j / inner4) * s_outer) + (j % inner4));
+        float4 h0, l0, h1, l1;
+        split4(x0, h0, l0);
+        split4(x1, h1, l1);
+        hi[i] = h0; lo[i] = l0;
+        hi[j] = h1; lo[j] = l1;
+    }
+    if (i < total) {
+        const float4 x0 = __ldg((const float4 *)(src + (i / inner4) * s_outer) + (i % inner4));
+        float4 h0, l0;
+        split4(x0, h0, l0);
+        hi[i] = h0; lo[i] = l0;
+    }
+}
+
 typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -396,6 +436,17 @@ bool g_attr_set = false;
 int split_tf32(const float *src, long s_outer, int outer, int inner, float *hi, float *lo, long ldp, cudaStream_t st) {
     size_t total = (size_t)outer * ldp;
     if (!total) return B2_OK;
+    if ((inner % 4) == 0 && ldp == inner && (s_outer % 4) == 0 && ((uintptr_t)src % 16) == 0 && ((uintptr_t)hi % 16) == 0 &&
+        ((uintptr_t)lo % 16) == 0) {
+        const size_t groups = total / 4;
+        size_t blocks = (groups + 511) / 512;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (blocks < 1) blocks = 1;
+        split_tf32_vec4_kernel<<<(int)blocks, 256, 0, st>>>(src, s_outer, outer, inner / 4, (float4 *)hi, (float4 *)lo);
+        count_launch();
+        B2_CUDA(cudaGetLastError());
+        return B2_OK;
+    }
     size_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     split_tf32_kernel<<<(int)blocks, 256, 0, st>>>(src, s_outer, outer, inner, hi, lo, ldp);

@@ -208,15 +208,15 @@ __global__ void wrec_transpose_kernel(int ls, int els, int D, const float *__res
 // Bias and peephole gradients: per unit u and frame chunk, partial sums of
 //   delta_g[f][u] (4 gates), c[f -/+ P]*delta_ig/fg[f] and c[f]*delta_og[f]
 // (layers/LstmLayer.cu:524-541,574-610 of the reference), then a fixed-order reduction.
-constexpr int VG_FR = 256;  // frames per chunk
-__global__ void lstm_vgrad_partial_kernel(LstmShape sh, LstmBuffers bf, float *__restrict__ ws) {
+__global__ void lstm_vgrad_partial_kernel(LstmShape sh, LstmBuffers bf, float *__restrict__ ws, int frames_per_chunk) {
     const int ls = sh.ls, els = sh.els, P = sh.P;
     const int u = blockIdx.x * blockDim.x + threadIdx.x;
     if (u >= ls) return;
     const int d = u / els;
     const long N = (long)sh.T * P;
-    long f0 = (long)blockIdx.y * VG_FR, f1 = min(N, f0 + VG_FR);
+    long f0 = (long)blockIdx.y * frames_per_chunk, f1 = min(N, f0 + frames_per_chunk);
     float s[7] = {0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 4
     for (long f = f0; f < f1; ++f) {
         const float *dl = bf.deltas + (size_t)f * 4 * ls + u;
         float dni = dl[0], dig = dl[ls], dfg = dl[2 * ls], dog = dl[3 * ls];
@@ -277,13 +277,17 @@ int lstm_backward_stepwise(const LstmShape &s, const LstmBuffers &b, const float
 int lstm_vector_grads(const LstmShape &s, const LstmBuffers &b, float *dw, float *ws, size_t ws_floats,
                       cudaStream_t st) {
     long N = (long)s.T * s.P;
-    int chunks = (int)((N + VG_FR - 1) / VG_FR);
-    if ((size_t)chunks * 7 * s.ls > ws_floats) {
+    // chunks of frames: enough blocks to fill the device several times over, bounded by the scratch
+    int fpc = 64;
+    const long max_chunks = (long)(ws_floats / ((size_t)7 * s.ls));
+    if (max_chunks < 1) {
         set_error("lstm_vector_grads: scratch too small");
         return B2_ERR_BAD_SHAPE;
     }
+    if ((N + fpc - 1) / fpc > max_chunks) fpc = (int)((N + max_chunks - 1) / max_chunks);
+    int chunks = (int)((N + fpc - 1) / fpc);
     dim3 grid((s.ls + 127) / 128, chunks);
-    lstm_vgrad_partial_kernel<<<grid, 128, 0, st>>>(s, b, ws);
+    lstm_vgrad_partial_kernel<<<grid, 128, 0, st>>>(s, b, ws, fpc);
     lstm_vgrad_reduce_kernel<<<(7 * s.ls + 255) / 256, 256, 0, st>>>(s, chunks, ws, dw);
     count_launch(2);
     B2_CUDA(cudaGetLastError());
