@@ -79,10 +79,11 @@ def workload_for(name, rank):
 
 
 # ---- algorithmic work per phase (per step, this rank) -----------------------------------------------
-def phase_work(layers, T, P, real_frames):
-    """{phase: (kind, amount)}: flops for GEMM phases (padded frames: the kernels process them),
-    bytes for HBM phases (40 B forward / 44 B backward per cell-step of a real or padded frame)."""
-    N = T * P
+def phase_work(layers, T, P, real_frames, count_padding=True):
+    """{phase: (kind, amount)}: flops for GEMM phases, bytes for HBM phases (40 B forward / 44 B
+    backward per cell-step).  count_padding: over all T*P frame slots (what the kernels process) or
+    over the real frames only (the algorithmic work the roofline is quoted on)."""
+    N = T * P if count_padding else real_frames
     w = {}
 
     def add(k, kind, v):
@@ -322,7 +323,7 @@ def main():
                         ent["tflops"] = round(fl[1] / (per * 1e-3) / 1e12, 3)
             kernels[name] = ent
         top = max((k for k in kernels if k in work), key=lambda k: kernels[k]["ms_per_step"])
-        kind, amt = work[top]
+        kind, amt = phase_work(layers, T, P, real_frames, count_padding=False)[top]   # real frames only
         per_launch = kernels[top]["ms_per_step"] * 1e-3
         if kind == "flops":
             peak = pk["bf16"] / 6.0   # 3xTF32: TF32 dense = bf16/2, three MMAs per fp32 product
@@ -332,7 +333,17 @@ def main():
             roof = {"bound": "hbm", "kernel": top, "achieved": amt / per_launch / 1e9, "peak": pk["hbm"], "unit": "GB/s",
                     "peak_note": "%s copy bandwidth" % pk["src"]}
         roof["frac"] = roof["achieved"] / roof["peak"]
-        roof["traffic"] = None
+        # DRAM bytes per launch of the dominant kernel, from the ncu capture summarised in
+        # profiles/lstm_persistent_kernels_cfg1_quarter_frames.md (bytes per unit and frame slot,
+        # scaled by the units x frame slots of one launch; traffic grows in proportion to the frames)
+        per_cell = {"lstm_fwd_recurrence": 28.7, "lstm_bwd_recurrence": 34.2}.get(top)
+        lstm_sizes = [l["size"] for l in layers if l["type"] in ("lstm", "blstm")]
+        if per_cell and lstm_sizes and args.workload == "cfg1" and args.recurrence == 1 and not args.ffma:
+            roof["traffic"] = per_cell * (sum(lstm_sizes) / len(lstm_sizes)) * T * P
+            roof["traffic_note"] = "bytes per launch (one layer's sweep), ncu dram__bytes scaled from a quarter-size capture"
+            roof["launches"] = len(lstm_sizes)
+        else:
+            roof["traffic"] = None
         roof["share_of_step"] = kernels[top]["share"]
         in_b = int(x_host.numel() * 4 + t_host.numel() * 4 + T * P)
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
