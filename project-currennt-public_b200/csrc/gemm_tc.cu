@@ -36,7 +36,7 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024; // + slack to align the 
 constexpr int NTHREADS = 192;
 constexpr int TC_MAX_BATCH = 8;
 constexpr int SEG = 2;                                  // slabs per drained accumulator segment
-constexpr int TMEM_COLS = 512;                          // 2 x 128 main accumulator + 128 cross terms (power of two)
+constexpr int TMEM_COLS = 512;                          // 2 x 128 main accumulator + 2 x 128 cross terms
 constexpr long long WAIT_CYCLES = 4000000000LL;         // about two seconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -133,43 +133,44 @@ struct TcArgs {
     // The contraction index may run over segments of kseg_len consecutive positions that lie
     // kseg_stride apart in both operands (the four gate blocks of one direction); 0 = contiguous.
     int kseg_len, kseg_stride;
+    // work items of the persistent tile loop: tiles_m x tiles_n output tiles x nz splits / batches
+    int tiles_m, tiles_n, nz;
 };
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
                    const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo, TcArgs a) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 4];
+    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 6];
     __shared__ uint32_t tmem_base_s;
-    __shared__ int fail_s;
+    __shared__ volatile int fail_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;   // SWIZZLE_128B atoms need 1024-byte alignment
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * (uint32_t)s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
-    // the main (hi*hi) accumulator is double-buffered in tensor memory and drained every SEG slabs
+    // the main (hi*hi) accumulator is double-buffered in tensor memory and drained every SEG slabs;
+    // the cross-term accumulator is double-buffered over tiles
     auto big_full = [&](int b) { return bar0 + 8u * (uint32_t)(2 * STAGES + b); };
     auto big_empty = [&](int b) { return bar0 + 8u * (uint32_t)(2 * STAGES + 2 + b); };
+    auto x_empty = [&](int b) { return bar0 + 8u * (uint32_t)(2 * STAGES + 4 + b); };
 
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-    const int zsplit = a.nbatch ? (int)blockIdx.z % a.splits : (int)blockIdx.z;
-    const int batch = a.nbatch ? (int)blockIdx.z / a.splits : 0;
-    const int a_in = a.nbatch ? a.a_off_inner[batch] : 0, a_out = a.nbatch ? a.a_off_outer[batch] : 0;
-    const int b_in = a.nbatch ? a.b_off_inner[batch] : 0, b_out = a.nbatch ? a.b_off_outer[batch] : 0;
-    const int kbeg = zsplit * a.kchunk;
-    const int kend = min(a.K, kbeg + a.kchunk);
-    const int nkb = (kend - kbeg + BK - 1) / BK;
+    // Persistent over work items (m tile fastest, then n tile, then split / batch): barriers and tensor
+    // memory are set up once per block, and the epilogue of one tile (global stores from registers)
+    // overlaps the MMAs of the next.
+    const int items = a.tiles_m * a.tiles_n * a.nz;
+    const int nkb_full = (a.kchunk + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(big_full(b), 1); mbar_init(big_empty(b), 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(big_full(b), 1); mbar_init(big_empty(b), 4); mbar_init(x_empty(b), 4); }
         fail_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void *)&tmem_base_s)), "r"(TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -181,33 +182,45 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-                if (!mbar_wait(empty_bar(s), ph ^ 1u)) { fail_s = 1; break; }
-                const uint32_t base = ring + (uint32_t)s * STAGE_BYTES;
-                int k0 = kbeg + kb * BK;
-                if (a.kseg_len) k0 = (k0 / a.kseg_len) * a.kseg_stride + k0 % a.kseg_len;   // segmented contraction index
-                mbar_expect_tx(full_bar(s), STAGE_BYTES);
-                // the contraction index is the inner coordinate of a K-major operand, the outer one otherwise
-                if (a.a_kmajor) {
-                    tma_load_2d(base, &mapAhi, k0 + a_in, m0 + a_out, full_bar(s));
-                    tma_load_2d(base + TILE_BYTES, &mapAlo, k0 + a_in, m0 + a_out, full_bar(s));
-                } else {
+            int kbg = 0;   // k-blocks issued by this block so far (ring position)
+            bool ok = true;
+            for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+                if (fail_s) break;
+                const int m0 = (item % a.tiles_m) * BM, n0 = ((item / a.tiles_m) % a.tiles_n) * BN;
+                const int z = item / (a.tiles_m * a.tiles_n);
+                const int zsplit = a.nbatch ? z % a.splits : z, batch = a.nbatch ? z / a.splits : 0;
+                const int a_in = a.nbatch ? a.a_off_inner[batch] : 0, a_out = a.nbatch ? a.a_off_outer[batch] : 0;
+                const int b_in = a.nbatch ? a.b_off_inner[batch] : 0, b_out = a.nbatch ? a.b_off_outer[batch] : 0;
+                const int kbeg = zsplit * a.kchunk;
+                const int nkb = min(nkb_full, (a.K - kbeg + BK - 1) / BK);
+                for (int kb = 0; kb < nkb; ++kb, ++kbg) {
+                    const int s = kbg % STAGES;
+                    const uint32_t ph = (uint32_t)(kbg / STAGES) & 1u;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u)) { fail_s = 1; ok = false; break; }
+                    const uint32_t base = ring + (uint32_t)s * STAGE_BYTES;
+                    int k0 = kbeg + kb * BK;
+                    if (a.kseg_len) k0 = (k0 / a.kseg_len) * a.kseg_stride + k0 % a.kseg_len;   // segmented contraction index
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    // the contraction index is the inner coordinate of a K-major operand, the outer one otherwise
+                    if (a.a_kmajor) {
+                        tma_load_2d(base, &mapAhi, k0 + a_in, m0 + a_out, full_bar(s));
+                        tma_load_2d(base + TILE_BYTES, &mapAlo, k0 + a_in, m0 + a_out, full_bar(s));
+                    } else {
 #pragma unroll
-                    for (int b = 0; b < BM / 32; ++b) {
-                        tma_load_2d(base + b * 4096, &mapAhi, m0 + 32 * b + a_in, k0 + a_out, full_bar(s));
-                        tma_load_2d(base + TILE_BYTES + b * 4096, &mapAlo, m0 + 32 * b + a_in, k0 + a_out, full_bar(s));
+                        for (int b = 0; b < BM / 32; ++b) {
+                            tma_load_2d(base + b * 4096, &mapAhi, m0 + 32 * b + a_in, k0 + a_out, full_bar(s));
+                            tma_load_2d(base + TILE_BYTES + b * 4096, &mapAlo, m0 + 32 * b + a_in, k0 + a_out, full_bar(s));
+                        }
                     }
-                }
-                if (a.b_kmajor) {
-                    tma_load_2d(base + 2 * TILE_BYTES, &mapBhi, k0 + b_in, n0 + b_out, full_bar(s));
-                    tma_load_2d(base + 3 * TILE_BYTES, &mapBlo, k0 + b_in, n0 + b_out, full_bar(s));
-                } else {
+                    if (a.b_kmajor) {
+                        tma_load_2d(base + 2 * TILE_BYTES, &mapBhi, k0 + b_in, n0 + b_out, full_bar(s));
+                        tma_load_2d(base + 3 * TILE_BYTES, &mapBlo, k0 + b_in, n0 + b_out, full_bar(s));
+                    } else {
 #pragma unroll
-                    for (int b = 0; b < BN / 32; ++b) {
-                        tma_load_2d(base + 2 * TILE_BYTES + b * 4096, &mapBhi, n0 + 32 * b + b_in, k0 + b_out, full_bar(s));
-                        tma_load_2d(base + 3 * TILE_BYTES + b * 4096, &mapBlo, n0 + 32 * b + b_in, k0 + b_out, full_bar(s));
+                        for (int b = 0; b < BN / 32; ++b) {
+                            tma_load_2d(base + 2 * TILE_BYTES + b * 4096, &mapBhi, n0 + 32 * b + b_in, k0 + b_out, full_bar(s));
+                            tma_load_2d(base + 3 * TILE_BYTES + b * 4096, &mapBlo, n0 + 32 * b + b_in, k0 + b_out, full_bar(s));
+                        }
                     }
                 }
             }
@@ -229,87 +242,115 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
             // length.  Two measures keep fp32 accuracy: the cross terms (2^-11 of the main term) get an
             // accumulator of their own, and the main accumulator is handed to the epilogue warps every
             // SEG slabs (SEG*4 MMAs), which add the segments in registers with round-to-nearest.
-            const uint32_t t_small = tmem_base + 2 * BN;
             bool ok = true;
-            const int nseg = (nkb + SEG - 1) / SEG;
-            for (int seg = 0; seg < nseg && ok; ++seg) {
-                const int buf = seg & 1;
-                const uint32_t use = (uint32_t)(seg >> 1);
-                if (!mbar_wait(big_empty(buf), (use & 1u) ^ 1u)) { fail_s = 1; ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t t_big = tmem_base + (uint32_t)buf * BN;
-                const int kb_end = min(nkb, (seg + 1) * SEG);
-                for (int kb = seg * SEG; kb < kb_end; ++kb) {
-                    const int s = kb % STAGES;
-                    const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-                    if (!mbar_wait(full_bar(s), ph)) { fail_s = 1; ok = false; break; }
+            int kbg = 0, gseg = 0, it = 0;
+            for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++it) {
+                if (fail_s) break;
+                const int z = item / (a.tiles_m * a.tiles_n);
+                const int zsplit = a.nbatch ? z % a.splits : z;
+                const int kbeg = zsplit * a.kchunk;
+                const int nkb = min(nkb_full, (a.K - kbeg + BK - 1) / BK);
+                const int xb = it & 1;
+                const uint32_t t_small = tmem_base + (uint32_t)(2 * BN + xb * BN);
+                // the cross-term accumulator of two tiles ago must have been read
+                if (!mbar_wait(x_empty(xb), ((uint32_t)(it >> 1) & 1u) ^ 1u)) { fail_s = 1; ok = false; break; }
+                const int nseg = (nkb + SEG - 1) / SEG;
+                for (int seg = 0; seg < nseg && ok; ++seg, ++gseg) {
+                    const int buf = gseg & 1;
+                    const uint32_t use = (uint32_t)(gseg >> 1);
+                    if (!mbar_wait(big_empty(buf), (use & 1u) ^ 1u)) { fail_s = 1; ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t base = ring + (uint32_t)s * STAGE_BYTES;
+                    const uint32_t t_big = tmem_base + (uint32_t)buf * BN;
+                    const int kb_end = min(nkb, (seg + 1) * SEG);
+                    for (int kb = seg * SEG; kb < kb_end; ++kb, ++kbg) {
+                        const int s = kbg % STAGES;
+                        const uint32_t ph = (uint32_t)(kbg / STAGES) & 1u;
+                        if (!mbar_wait(full_bar(s), ph)) { fail_s = 1; ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t base = ring + (uint32_t)s * STAGE_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < BK / 8; ++kk) {
-                        const unsigned long long ahi = make_desc(base + kk * a_step, a_lbo, a_sbo, a_lt);
-                        const unsigned long long alo = make_desc(base + TILE_BYTES + kk * a_step, a_lbo, a_sbo, a_lt);
-                        const unsigned long long bhi = make_desc(base + 2 * TILE_BYTES + kk * b_step, b_lbo, b_sbo, b_lt);
-                        const unsigned long long blo = make_desc(base + 3 * TILE_BYTES + kk * b_step, b_lbo, b_sbo, b_lt);
-                        mma_tf32(t_small, alo, bhi, idesc, (kb | kk) ? 1u : 0u);
-                        mma_tf32(t_small, ahi, blo, idesc, 1u);
-                        mma_tf32(t_big, ahi, bhi, idesc, (kb != seg * SEG || kk) ? 1u : 0u);
+                        for (int kk = 0; kk < BK / 8; ++kk) {
+                            const unsigned long long ahi = make_desc(base + kk * a_step, a_lbo, a_sbo, a_lt);
+                            const unsigned long long alo = make_desc(base + TILE_BYTES + kk * a_step, a_lbo, a_sbo, a_lt);
+                            const unsigned long long bhi = make_desc(base + 2 * TILE_BYTES + kk * b_step, b_lbo, b_sbo, b_lt);
+                            const unsigned long long blo = make_desc(base + 3 * TILE_BYTES + kk * b_step, b_lbo, b_sbo, b_lt);
+                            mma_tf32(t_small, alo, bhi, idesc, (kb | kk) ? 1u : 0u);
+                            mma_tf32(t_small, ahi, blo, idesc, 1u);
+                            mma_tf32(t_big, ahi, bhi, idesc, (kb != seg * SEG || kk) ? 1u : 0u);
+                        }
+                        mma_commit(empty_bar(s));   // slot is free once these MMAs have read it
                     }
-                    mma_commit(empty_bar(s));   // slot is free once these MMAs have read it
+                    mma_commit(big_full(buf));      // everything issued so far (cross terms included) is complete
                 }
-                mma_commit(big_full(buf));      // everything issued so far (cross terms included) is complete
             }
         }
     } else {
         // ---------------- epilogue: drain segments from TMEM, sum in registers, write C ----------------
         const int q = warp & 3;             // TMEM lane quarter this warp may read
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
-        float acc[BN];
-#pragma unroll
-        for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
-        const int nseg = (nkb + SEG - 1) / SEG;
         bool ok = true;
-        for (int seg = 0; seg < nseg; ++seg) {
-            const int buf = seg & 1;
-            const uint32_t use = (uint32_t)(seg >> 1);
-            ok = __all_sync(0xffffffffu, mbar_wait(big_full(buf), use & 1u));
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        int gseg = 0, it = 0;
+        for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++it) {
+            if (fail_s) break;
+            const int m0 = (item % a.tiles_m) * BM, n0 = ((item / a.tiles_m) % a.tiles_n) * BN;
+            const int z = item / (a.tiles_m * a.tiles_n);
+            const int zsplit = a.nbatch ? z % a.splits : z, batch = a.nbatch ? z / a.splits : 0;
+            const int kbeg = zsplit * a.kchunk;
+            const int nkb = min(nkb_full, (a.K - kbeg + BK - 1) / BK);
+            const int xb = it & 1;
+            float acc[BN];
+#pragma unroll
+            for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
+            const int nseg = (nkb + SEG - 1) / SEG;
+            for (int seg = 0; seg < nseg; ++seg, ++gseg) {
+                const int buf = gseg & 1;
+                const uint32_t use = (uint32_t)(gseg >> 1);
+                ok = __all_sync(0xffffffffu, mbar_wait(big_full(buf), use & 1u));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(lane_base + (uint32_t)(buf * BN + c0), r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(big_empty(buf)) : "memory");
+            }
+            if (!ok) {
+                if (lane == 0) fail_s = 1;
+                break;
+            }
+            // the cross terms: complete with the last segment's commit; after this read tensor memory is
+            // free for the tile after next, and the stores below run under the next tile's MMAs
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld32(lane_base + (uint32_t)(buf * BN + c0), r);
+                tmem_ld32(lane_base + (uint32_t)(2 * BN + xb * BN + c0), r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(big_empty(buf)) : "memory");
-        }
-        if (!ok) {
-            if (lane == 0) fail_s = 1;
-        } else {
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(x_empty(xb)) : "memory");
+
             const int m = m0 + 32 * q + lane;
             const bool batched = a.nbatch > 0;
-            const bool split = !batched && gridDim.z > 1;
+            const bool split = !batched && a.nz > 1;
             float *dst = batched ? a.C + a.c_off[batch] + (long long)zsplit * a.c_split_stride
-                                 : (split ? a.ws + (size_t)blockIdx.z * (size_t)a.M * a.N : a.C);
+                                 : (split ? a.ws + (size_t)z * (size_t)a.M * a.N : a.C);
             const long ld = split ? (long)a.M : a.ldc;
+            if (m < a.M) {
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + (uint32_t)(2 * BN + c0), r);     // the cross-term accumulator
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (m < a.M) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int n = n0 + c0 + j;
-                        if (n < a.N) {
-                            float *p = dst + (size_t)n * ld + m;
-                            float v = acc[c0 + j] + __uint_as_float(r[j]);
-                            if (!split && !batched && a.accumulate) v += *p;
-                            *p = v;
-                        }
+                for (int j = 0; j < BN; ++j) {
+                    const int n = n0 + j;
+                    if (n < a.N) {
+                        float *p = dst + (size_t)n * ld + m;
+                        float v = acc[j];
+                        if (!split && !batched && a.accumulate) v += *p;
+                        *p = v;
                     }
                 }
             }
@@ -430,6 +471,17 @@ int make_map(CUtensorMap *map, const float *base, long inner, long outer, long l
 }
 
 bool g_attr_set = false;
+int g_sm_count = 0;
+
+// one block per SM (the kernel loops over its share of the tiles), fewer when there is less work
+int persistent_grid(int items) {
+    if (!g_sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sm_count < 1) g_sm_count = 148;
+    }
+    return items < g_sm_count ? items : g_sm_count;
+}
 
 }  // namespace
 
@@ -492,13 +544,24 @@ int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, in
     // Split K to fill the 148 SMs when there are few output tiles; the partial sums are added with
     // fp32 FADD in a fixed order.
     int splits = 1;
-    if (ws) {
-        if (tiles < 148 && k >= 1024) splits = (148 + tiles - 1) / tiles;
-        const int maxs = (k + 255) / 256;
-        if (splits > maxs) splits = maxs;
+    if (ws && k >= 1024) {
+        // Model of the persistent kernel: every block runs ceil(items / SMs) tiles of k/splits slabs
+        // (about 0.4 us per slab and 3 us per tile), then the partial sums cost a pass over
+        // splits * m * n floats.  Pick the split count with the smallest estimate.
+        const int sms = persistent_grid(1 << 30);
         const size_t per = (size_t)m * n;
-        if ((size_t)splits * per > ws_floats) splits = (int)(ws_floats / per);
-        if (splits < 1) splits = 1;
+        int maxs = (k + 255) / 256;
+        if (maxs > 64) maxs = 64;
+        if ((size_t)maxs * per > ws_floats) maxs = (int)(ws_floats / per);
+        double best = 0.0;
+        for (int sp = 1; sp <= maxs; ++sp) {
+            const int items = tiles * sp;
+            const int waves = (items + sms - 1) / sms;
+            const double slabs = (double)((k + sp - 1) / sp + BK - 1) / BK;
+            double t = waves * (0.4 * slabs + 3.0);
+            if (sp > 1) t += 4.0 + (double)sp * per * 8.0 / 5.0e6;   // write + read of the partials at ~5 TB/s, in us
+            if (sp == 1 || t < best) { best = t; splits = sp; }
+        }
     }
     int kchunk = (k + splits - 1) / splits;
     kchunk = (kchunk + BK - 1) / BK * BK;
@@ -509,7 +572,8 @@ int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, in
     a.a_kmajor = A.kmajor ? 1 : 0; a.b_kmajor = B.kmajor ? 1 : 0;
     a.accumulate = accumulate ? 1 : 0; a.ws = ws; a.status = status;
     a.nbatch = 0; a.splits = splits; a.c_split_stride = 0; a.kseg_len = 0; a.kseg_stride = 0;
-    gemm_tf32x3_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(mAh, mAl, mBh, mBl, a);
+    a.tiles_m = (int)grid.x; a.tiles_n = (int)grid.y; a.nz = splits;
+    gemm_tf32x3_kernel<<<persistent_grid(a.tiles_m * a.tiles_n * a.nz), NTHREADS, SMEM_BYTES, st>>>(mAh, mAl, mBh, mBl, a);
     count_launch();
     B2_CUDA(cudaGetLastError());
     if (splits > 1) {
@@ -570,9 +634,8 @@ int tc_plan_launch(const TcPlan *p, float *C, const TcBatch *batches, int nbatch
         a.b_off_inner[b] = batches[b].b_in; a.b_off_outer[b] = batches[b].b_out;
         a.c_off[b] = batches[b].c_off;
     }
-    dim3 grid = p->grid;
-    grid.z = nbatch * a.splits;
-    gemm_tf32x3_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(p->mAh, p->mAl, p->mBh, p->mBl, a);
+    a.tiles_m = (int)p->grid.x; a.tiles_n = (int)p->grid.y; a.nz = nbatch * a.splits;
+    gemm_tf32x3_kernel<<<persistent_grid(a.tiles_m * a.tiles_n * a.nz), NTHREADS, SMEM_BYTES, st>>>(p->mAh, p->mAl, p->mBh, p->mBl, a);
     count_launch();
     B2_CUDA(cudaGetLastError());
     return B2_OK;
