@@ -35,7 +35,7 @@ constexpr int STAGE_BYTES = 4 * TILE_BYTES;             // A_hi, A_lo, B_hi, B_l
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024; // + slack to align the ring to 1024 B
 constexpr int NTHREADS = 192;
 constexpr int TC_MAX_BATCH = 8;
-constexpr int SEG = 2;                                  // slabs per drained accumulator segment
+constexpr int SEG = 4;                                  // slabs per drained accumulator segment
 constexpr int TMEM_COLS = 512;                          // 2 x 128 main accumulator + 2 x 128 cross terms
 constexpr long long WAIT_CYCLES = 4000000000LL;         // about two seconds
 
