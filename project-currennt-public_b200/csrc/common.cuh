@@ -87,6 +87,11 @@ int tc_plan_create(TcPlan **out, const SplitOperand &A, long a_inner, long a_out
 int tc_plan_launch(const TcPlan *p, float *C, const TcBatch *batches, int nbatch, long long c_split_stride, int *status,
                    cudaStream_t st);
 void tc_plan_destroy(TcPlan *p);
+// sums the K-split partials a batched launch wrote to ws (batch b, split z at (b*splits + z)*m*n) into
+// C + c_off[b] with leading dimension ldc
+int tc_batched_reduce(float *C, const long long *c_off, int nbatch, long ldc, const float *ws, int m, int n, int splits,
+                      cudaStream_t st);
+int tc_sm_count();
 bool gemm_wants_tc(long sam, long sak, long sbk, long sbn, int m, int n, int k);
 // picks the tensor-core kernel when the shape qualifies (and sc/status are given), else FFMA
 int gemm_auto(float *C, long ldc, const float *A, long sam, long sak, const float *B, long sbk, long sbn, int m, int n,

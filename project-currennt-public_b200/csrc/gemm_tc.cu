@@ -376,6 +376,22 @@ __global__ void tc_splitk_reduce_kernel(float *__restrict__ C, long ldc, const f
     }
 }
 
+// sums the K-split partials of a batched launch: batch b, split z at ws[(b*splits + z)*M*N ...] (leading
+// dimension M) -> C + c_off[b] (leading dimension ldc), fixed order
+struct BatchOffsets { long long c_off[TC_MAX_BATCH]; };
+__global__ void tc_batched_reduce_kernel(float *__restrict__ C, BatchOffsets off, long ldc, const float *__restrict__ ws, int M,
+                                         int N, int splits, int nbatch) {
+    const size_t per = (size_t)M * N, total = per * nbatch;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int b = (int)(i / per);
+        const size_t e = i % per;
+        const float *p = ws + (size_t)b * splits * per + e;
+        float s = 0.0f;
+        for (int z = 0; z < splits; ++z) s += p[(size_t)z * per];
+        C[off.c_off[b] + (long long)(e / M) * ldc + (long long)(e % M)] = s;
+    }
+}
+
 // hi = rn_tf32(x), lo = rn_tf32(x - hi); dense destination [outer][ldp], zero padded to ldp
 __global__ void split_tf32_kernel(const float *__restrict__ src, long s_outer, int outer, int inner, float *__restrict__ hi,
                                   float *__restrict__ lo, long ldp) {
@@ -602,7 +618,9 @@ int tc_plan_create(TcPlan **out, const SplitOperand &A, long a_inner, long a_out
         B2_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         g_attr_set = true;
     }
-    if (splits < 1 || (k % (splits * BK)) != 0 || (kseg_len && (kseg_len % BK) != 0)) {
+    // a segmented contraction index needs whole slabs per split; a contiguous one may be ragged (the
+    // tensor maps fill the overhang with zeros as long as one operand's extent ends at k)
+    if (splits < 1 || (kseg_len && ((k % (splits * BK)) != 0 || (kseg_len % BK) != 0))) {
         set_error("tc_plan_create: k=%d must divide into %d splits of whole %d-slabs (segment %d)", k, splits, BK, kseg_len);
         return B2_ERR_BAD_SHAPE;
     }
@@ -614,7 +632,13 @@ int tc_plan_create(TcPlan **out, const SplitOperand &A, long a_inner, long a_out
     if (rc != B2_OK) { delete p; return rc; }
     TcArgs &a = p->args;
     a = TcArgs{};
-    a.ldc = ldc; a.M = m; a.N = n; a.K = k; a.kchunk = k / splits;
+    a.ldc = ldc; a.M = m; a.N = n; a.K = k;
+    a.kchunk = ((k + splits - 1) / splits + BK - 1) / BK * BK;
+    if ((long)a.kchunk * (splits - 1) >= k) {
+        set_error("tc_plan_create: %d splits leave an empty split for k=%d", splits, k);
+        delete p;
+        return B2_ERR_BAD_SHAPE;
+    }
     a.a_kmajor = A.kmajor ? 1 : 0; a.b_kmajor = B.kmajor ? 1 : 0;
     a.splits = splits; a.kseg_len = kseg_len; a.kseg_stride = kseg_stride;
     p->grid = dim3((m + BM - 1) / BM, (n + BN - 1) / BN, 1);
@@ -623,6 +647,22 @@ int tc_plan_create(TcPlan **out, const SplitOperand &A, long a_inner, long a_out
 }
 
 void tc_plan_destroy(TcPlan *p) { delete p; }
+
+int tc_batched_reduce(float *C, const long long *c_off, int nbatch, long ldc, const float *ws, int m, int n, int splits,
+                      cudaStream_t st) {
+    if (nbatch < 1 || nbatch > TC_MAX_BATCH) { set_error("tc_batched_reduce: 1..%d batches", TC_MAX_BATCH); return B2_ERR_BAD_ARG; }
+    BatchOffsets off;
+    for (int b = 0; b < nbatch; ++b) off.c_off[b] = c_off[b];
+    const size_t total = (size_t)m * n * nbatch;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    tc_batched_reduce_kernel<<<blocks, 256, 0, st>>>(C, off, ldc, ws, m, n, splits, nbatch);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int tc_sm_count() { return persistent_grid(1 << 30); }
 
 int tc_plan_launch(const TcPlan *p, float *C, const TcBatch *batches, int nbatch, long long c_split_stride, int *status,
                    cudaStream_t st) {

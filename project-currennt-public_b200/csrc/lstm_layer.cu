@@ -186,7 +186,43 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
     {
         Phase ph(*this, "lstm_dw_rec_gemm");
         const bool tc_rec = tc && (els % 4) == 0 && gemm_wants_tc(1, ls, 4 * ls, 1, els, els, K);
-        for (int d = 0; d < D; ++d)
+        bool done = false;
+        if (tc_rec && 4 * D <= 8) {
+            // all 4*D products in ONE batched launch: batch = (direction, gate); K is split so that the
+            // work items fill a whole number of waves; partial sums go to scratch and are added in fixed order
+            const int tiles = ((els + 127) / 128) * ((els + 127) / 128) * 4 * D;
+            const int sms = tc_sm_count();
+            const size_t per = (size_t)els * els;
+            int splits = 0;
+            double best = 0.0;
+            for (int sp = 1; sp <= 64 && (size_t)sp * 4 * D * per <= ws_floats && (long)sp * 256 <= K; ++sp) {
+                const int waves = (tiles * sp + sms - 1) / sms;
+                const double t = waves * (0.4 * ((K + sp - 1) / sp) / 32.0 + 3.0) + (double)sp * 4 * D * per * 8.0 / 5.0e6;
+                if (!splits || t < best) { best = t; splits = sp; }
+            }
+            if (splits >= 1) {
+                SplitOperand A = sY, B = sD;
+                A.kmajor = false; B.kmajor = false;
+                TcPlan *plan = nullptr;
+                B2_TRY(tc_plan_create(&plan, A, ls, N, B, 4L * ls, N, els, els, K, splits, 0, 0, els));
+                TcBatch bt[8];
+                long long coff[8];
+                for (int d = 0; d < D; ++d)
+                    for (int g = 0; g < 4; ++g) {
+                        TcBatch &b = bt[d * 4 + g];
+                        b.a_in = d * els; b.a_out = d ? P : 0;                 // h of the previous step in sweep order
+                        b.b_in = g * ls + d * els; b.b_out = d ? 0 : P;
+                        b.c_off = (long long)(d * 4 + g) * splits * (long long)per;
+                        coff[d * 4 + g] = (long long)(off.rec + ((size_t)g * ls + (size_t)d * els) * els);
+                    }
+                int rc = tc_plan_launch(plan, ws, bt, 4 * D, (long long)per, status_dev, st);
+                tc_plan_destroy(plan);
+                B2_TRY(rc);
+                B2_TRY(tc_batched_reduce(dw, coff, 4 * D, els, ws, els, els, splits, st));
+                done = true;
+            }
+        }
+        for (int d = 0; d < D && !done; ++d)
             for (int g = 0; g < 4; ++g) {
                 float *C = dw + off.rec + ((size_t)g * ls + (size_t)d * els) * els;
                 if (tc_rec) {
