@@ -67,13 +67,22 @@ __global__ void column_sums_partial_kernel(float *__restrict__ ws, const float *
     for (long r = r0; r < r1; ++r) s += m[(size_t)r * ld + u];
     ws[(size_t)blockIdx.y * cols + u] = s;
 }
-__global__ void column_sums_reduce_kernel(float *__restrict__ out, const float *__restrict__ ws, int cols, int chunks,
-                                          float scale) {
-    int u = blockIdx.x * blockDim.x + threadIdx.x;
-    if (u >= cols) return;
+// 32 columns x 8 chunk phases per block: phase y adds chunks y, y+8, ...; the 8 sums are added in fixed order
+__global__ void __launch_bounds__(256) column_sums_reduce_kernel(float *__restrict__ out, const float *__restrict__ ws, int cols,
+                                                                 int chunks, float scale) {
+    __shared__ float part[8][33];
+    const int u = blockIdx.x * 32 + threadIdx.x;
     float s = 0.0f;
-    for (int c = 0; c < chunks; ++c) s += ws[(size_t)c * cols + u];
-    out[u] = scale * s;
+    if (u < cols)
+        for (int c = threadIdx.y; c < chunks; c += 8) s += ws[(size_t)c * cols + u];
+    part[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && u < cols) {
+        float t = 0.0f;
+#pragma unroll
+        for (int y = 0; y < 8; ++y) t += part[y][threadIdx.x];
+        out[u] = scale * t;
+    }
 }
 
 __global__ void sse_partial_kernel(double *__restrict__ ws, const float *__restrict__ y, const float *__restrict__ tgt,
@@ -168,7 +177,7 @@ int column_sums(float *out, const float *m, long ld, int cols, long rows, float 
     if (chunks < 1) chunks = 1;
     dim3 grid((cols + 127) / 128, chunks);
     column_sums_partial_kernel<<<grid, 128, 0, st>>>(ws, m, ld, cols, rows, rpc);
-    column_sums_reduce_kernel<<<(cols + 127) / 128, 128, 0, st>>>(out, ws, cols, chunks, scale);
+    column_sums_reduce_kernel<<<(cols + 31) / 32, dim3(32, 8), 0, st>>>(out, ws, cols, chunks, scale);
     count_launch(2);
     B2_CUDA(cudaGetLastError());
     return B2_OK;

@@ -234,16 +234,25 @@ __global__ void lstm_vgrad_partial_kernel(LstmShape sh, LstmBuffers bf, float *_
 #pragma unroll
     for (int i = 0; i < 7; ++i) o[(size_t)i * ls + u] = s[i];
 }
-__global__ void lstm_vgrad_reduce_kernel(LstmShape sh, int chunks, const float *__restrict__ ws, float *__restrict__ dw) {
+// 32 entries x 8 chunk phases per block; fixed summation order
+__global__ void __launch_bounds__(256) lstm_vgrad_reduce_kernel(LstmShape sh, int chunks, const float *__restrict__ ws,
+                                                                float *__restrict__ dw) {
+    __shared__ float part[8][33];
     const int ls = sh.ls;
-    int i = blockIdx.x * blockDim.x + threadIdx.x;  // 0 .. 7*ls
-    if (i >= 7 * ls) return;
+    const int i = blockIdx.x * 32 + threadIdx.x;  // 0 .. 7*ls
     float s = 0.0f;
-    for (int c = 0; c < chunks; ++c) s += ws[(size_t)c * 7 * ls + i];
+    if (i < 7 * ls)
+        for (int c = threadIdx.y; c < chunks; c += 8) s += ws[(size_t)c * 7 * ls + i];
+    part[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y != 0 || i >= 7 * ls) return;
+    float t = 0.0f;
+#pragma unroll
+    for (int y = 0; y < 8; ++y) t += part[y][threadIdx.x];
     const LstmOffsets off = lstm_offsets(sh.pls, ls, sh.els);
     int which = i / ls, u = i % ls;
-    if (which < 4) dw[off.bias + (size_t)which * ls + u] = sh.bias * s;
-    else dw[off.peep + (size_t)(which - 4) * ls + u] = s;
+    if (which < 4) dw[off.bias + (size_t)which * ls + u] = sh.bias * t;
+    else dw[off.peep + (size_t)(which - 4) * ls + u] = t;
 }
 
 }  // namespace
@@ -288,7 +297,7 @@ int lstm_vector_grads(const LstmShape &s, const LstmBuffers &b, float *dw, float
     int chunks = (int)((N + fpc - 1) / fpc);
     dim3 grid((s.ls + 127) / 128, chunks);
     lstm_vgrad_partial_kernel<<<grid, 128, 0, st>>>(s, b, ws, fpc);
-    lstm_vgrad_reduce_kernel<<<(7 * s.ls + 255) / 256, 256, 0, st>>>(s, chunks, ws, dw);
+    lstm_vgrad_reduce_kernel<<<(7 * s.ls + 31) / 32, dim3(32, 8), 0, st>>>(s, chunks, ws, dw);
     count_launch(2);
     B2_CUDA(cudaGetLastError());
     return B2_OK;
