@@ -134,6 +134,23 @@ def test_persistent_geometries(ls, bi, P, lens, variant):
     parity.compare_run(layers, got, want, "ls%d bi%d P%d" % (ls, bi, P), lstm_pad_zero_lens=lens)
 
 
+@pytest.mark.parametrize("variant", [VARIANTS[2], VARIANTS[5]], ids=[VARIANT_IDS[2], VARIANT_IDS[5]])
+@pytest.mark.parametrize("ls,bi,P,lens", [(320, 1, 8, [40] * 6 + [33, 21]), (200, 0, 6, [50, 50, 47, 30, 22, 9]),
+                                          (150, 0, 5, [60, 55, 50, 45, 40]), (384, 1, 4, [70, 64, 31, 70])])
+def test_unit_counts_that_do_not_fill_tiles(ls, bi, P, lens, variant):
+    """Units per direction that are no multiple of the 128-wide GEMM tile (160, 200, 150, 192) with
+    products large enough for the tensor-core kernels: the batched recurrent-weight-gradient launch reads
+    tiles that hang over into the other direction's columns and must not let them leak into the result."""
+    from b2lstm import workloads
+    layers = L(("input", 24), ("blstm" if bi else "lstm", ls), ("feedforward_identity", 8), ("sse", 8))
+    lens = np.array(lens, np.int32)
+    x, tg = workloads.make_fraction(24, 8, P, lens, 41, 42)
+    w = workloads.make_weights(layers, 43, 0.05)
+    want = run_kind(checker(), layers, P, lens, x, tg, w)
+    got = run_gpu(layers, P, lens, x, tg, w, variant)
+    parity.compare_run(layers, got, want, "ls%d bi%d P%d" % (ls, bi, P), lstm_pad_zero_lens=lens)
+
+
 def test_reuse_across_fractions_of_different_length():
     """A net sized for the longest fraction processes shorter and longer fractions back to back
     (stale state in the buffers must not leak into the next fraction)."""
