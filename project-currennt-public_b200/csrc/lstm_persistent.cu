@@ -719,10 +719,6 @@ int persistent_ps(int els, int P, int D, bool use_cluster) {
     int JB;
     if (!persistent_geometry(els, &JB)) return 0;
     if (P == 1) return 1;
-    if (const char *e = getenv("B2_PS")) {   // experiments only: force the sequences per work item
-        int v = atoi(e);
-        if (v == 4 || v == 8 || (v == 16 && els < 1024)) return v;
-    }
     const int G = els / JB;
     int slots = num_sms() / G;
     if (use_cluster && persistent_cluster_slots(els) > 0) slots = persistent_cluster_slots(els);
