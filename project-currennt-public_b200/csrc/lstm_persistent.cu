@@ -305,46 +305,36 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
                 const int c = tid + ci * NT;
                 if (c >= CELLS) continue;
                 const int p = c / JB, jj = c % JB;
-                float h = 0.0f;
-                if (mode[ci] != 2) {
-                    const size_t f = (size_t)t * P + (p0 + p);
-                    const int u = d * ELS + j0 + jj;
-                    float *ap = a.bf.acts + f * 4 * ls + u;
-                    if (mode[ci] == 1) {
-                        ap[0] = 0.0f; ap[ls] = 0.0f; ap[2 * (size_t)ls] = 0.0f; ap[3 * (size_t)ls] = 0.0f;
-                        a.bf.cells[f * ls + u] = 0.0f;
-                        cprev[ci] = 0.0f;
-                    } else {
-                        float rec[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                        if (!first) {
-                            if constexpr (NPARTF > 1) {
+                float h = 0.0f, ni = 0.0f, ig = 0.0f, fg = 0.0f, og = 0.0f, cs = 0.0f;
+                if (mode[ci] == 1) {
+                    cprev[ci] = 0.0f;
+                } else if (mode[ci] == 0) {
+                    float rec[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    if (!first) {
+                        if constexpr (NPARTF > 1) {
 #pragma unroll
-                                for (int q = 0; q < 4; ++q)
+                            for (int q = 0; q < 4; ++q)
 #pragma unroll
-                                    for (int k2 = 0; k2 < NPARTF; ++k2) rec[q] += red2[k2 * 4 * CELLS + (q * PS + p) * JB + jj];
-                            } else {
+                                for (int k2 = 0; k2 < NPARTF; ++k2) rec[q] += red2[k2 * 4 * CELLS + (q * PS + p) * JB + jj];
+                        } else {
 #pragma unroll
-                                for (int q = 0; q < 4; ++q)
+                            for (int q = 0; q < 4; ++q)
 #pragma unroll 8
-                                    for (int k2 = 0; k2 < KSPLIT; ++k2) rec[q] += red[((k2 * 4 + q) * PS + p) * JB + jj];
-                            }
+                                for (int k2 = 0; k2 < KSPLIT; ++k2) rec[q] += red[((k2 * 4 + q) * PS + p) * JB + jj];
                         }
-                        float ni = a4[ci][0] + rec[0] + b4[ci][0];
-                        float ig = a4[ci][1] + rec[1] + b4[ci][1];
-                        float fg = a4[ci][2] + rec[2] + b4[ci][2];
-                        float og = a4[ci][3] + rec[3] + b4[ci][3];
-                        const float cp = cprev[ci];
-                        if (!first) { ig += cp * pw[ci][0]; fg += cp * pw[ci][1]; }
-                        ni = act_tanh(ni); ig = act_logistic(ig); fg = act_logistic(fg);
-                        float cs = ni * ig;
-                        if (!first) cs += cp * fg;
-                        og = act_logistic(og + cs * pw[ci][2]);
-                        h = act_tanh(cs) * og;
-                        ap[0] = ni; ap[ls] = ig; ap[2 * (size_t)ls] = fg; ap[3 * (size_t)ls] = og;
-                        a.bf.cells[f * ls + u] = cs;
-                        cprev[ci] = cs;
                     }
-                    a.y[f * ls + u] = h;
+                    ni = a4[ci][0] + rec[0] + b4[ci][0];
+                    ig = a4[ci][1] + rec[1] + b4[ci][1];
+                    fg = a4[ci][2] + rec[2] + b4[ci][2];
+                    og = a4[ci][3] + rec[3] + b4[ci][3];
+                    const float cp = cprev[ci];
+                    if (!first) { ig += cp * pw[ci][0]; fg += cp * pw[ci][1]; }
+                    ni = act_tanh(ni); ig = act_logistic(ig); fg = act_logistic(fg);
+                    cs = ni * ig;
+                    if (!first) cs += cp * fg;
+                    og = act_logistic(og + cs * pw[ci][2]);
+                    h = act_tanh(cs) * og;
+                    cprev[ci] = cs;
                 }
                 if constexpr (CL) {
                     const uint32_t la = smem_addr(hs_all + (s & 1) * ELS * PS + (j0 + jj) * PS + p);
@@ -352,6 +342,15 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
                     for (int rk = 0; rk < G; ++rk) st_remote(map_to_rank(la, (uint32_t)rk), h);
                 } else {
                     st_pair(xo + (size_t)p * ELS + j0 + jj, h, tag0 + (unsigned)s + 1u);
+                }
+                // the peers are waiting for h: the layer's own state goes to memory after it is on its way
+                if (mode[ci] != 2) {
+                    const size_t f = (size_t)t * P + (p0 + p);
+                    const int u = d * ELS + j0 + jj;
+                    float *ap = a.bf.acts + f * 4 * ls + u;
+                    ap[0] = ni; ap[ls] = ig; ap[2 * (size_t)ls] = fg; ap[3 * (size_t)ls] = og;   // zeros on padding frames
+                    a.bf.cells[f * ls + u] = cs;
+                    a.y[f * ls + u] = h;
                 }
             }
             if constexpr (CL) cluster_arrive();
@@ -481,6 +480,18 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
                 }
             }
             // 3. cell errors and gate deltas (ComputeBlockErrorsFn)
+            float dd[CPT][4];
+            // the deltas go to memory after the partial sums the peers wait for have been sent
+            auto store_deltas = [&]() {
+#pragma unroll
+                for (int ci = 0; ci < CPT; ++ci) {
+                    const int c = tid + ci * NT;
+                    if (c >= CELLS || mode[ci] == 2) continue;
+                    const size_t f = (size_t)t * P + (p0 + c / JB);
+                    float *dl = a.bf.deltas + f * 4 * ls + d * ELS + j0 + (c % JB);
+                    dl[0] = dd[ci][0]; dl[ls] = dd[ci][1]; dl[2 * (size_t)ls] = dd[ci][2]; dl[3 * (size_t)ls] = dd[ci][3];
+                }
+            };
 #pragma unroll
             for (int ci = 0; ci < CPT; ++ci) {
                 const int c = tid + ci * NT;
@@ -513,17 +524,13 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
                 }
                 st_ce[ci] = ce; st_dig[ci] = dig; st_dfg[ci] = dfg;
                 c_keep[ci] = cpv[ci];   // c[prevc] is the next step's own cell state
-                if (mode[ci] != 2) {
-                    const size_t f = (size_t)t * P + (p0 + p);
-                    float *dl = a.bf.deltas + f * 4 * ls + d * ELS + j0 + jj;
-                    dl[0] = dni; dl[ls] = dig; dl[2 * (size_t)ls] = dfg; dl[3 * (size_t)ls] = dog;
-                }
+                dd[ci][0] = dni; dd[ci][1] = dig; dd[ci][2] = dfg; dd[ci][3] = dog;
                 ds[(0 * JB + jj) * PS + p] = dni;
                 ds[(1 * JB + jj) * PS + p] = dig;
                 ds[(2 * JB + jj) * PS + p] = dfg;
                 ds[(3 * JB + jj) * PS + p] = dog;
             }
-            if (lastCall) break;
+            if (lastCall) { store_deltas(); break; }
             __syncthreads();
             // 4. this block's contribution to the output error of every unit k at the next step
             u64 *xo = xitem + (size_t)(s & 1) * XBUF;
@@ -580,6 +587,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
                 for (int q = 0; q < RSPLIT; ++q) v += redb[(size_t)(q * PS + p) * ELS + k];
                 send(k, p, v);
             }
+            store_deltas();
             if constexpr (CL) cluster_arrive();
         }
         // item boundary: nobody may overwrite a buffer (or leave the kernel) while a peer still reads it
