@@ -29,7 +29,7 @@
 namespace b2 {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3;
+constexpr int BM = 128, BK = 32, STAGES = 3;   // the tile's N extent is a template parameter: 128, or 64 for narrow products
 constexpr int TILE_BYTES = BM * BK * 4;                 // 16 KiB: one operand part (hi or lo) of one stage
 constexpr int STAGE_BYTES = 4 * TILE_BYTES;             // A_hi, A_lo, B_hi, B_lo
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024; // + slack to align the ring to 1024 B
@@ -137,6 +137,7 @@ struct TcArgs {
     int tiles_m, tiles_n, nz;
 };
 
+template <int BN>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
                    const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo, TcArgs a) {
@@ -200,7 +201,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
                     const uint32_t base = ring + (uint32_t)s * STAGE_BYTES;
                     int k0 = kbeg + kb * BK;
                     if (a.kseg_len) k0 = (k0 / a.kseg_len) * a.kseg_stride + k0 % a.kseg_len;   // segmented contraction index
-                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    mbar_expect_tx(full_bar(s), 2 * TILE_BYTES + 2 * BN * BK * 4);
                     // the contraction index is the inner coordinate of a K-major operand, the outer one otherwise
                     if (a.a_kmajor) {
                         tma_load_2d(base, &mapAhi, k0 + a_in, m0 + a_out, full_bar(s));
@@ -490,6 +491,7 @@ bool g_attr_set = false;
 int g_sm_count = 0;
 
 // one block per SM (the kernel loops over its share of the tiles), fewer when there is less work
+int set_kernel_attributes();
 int persistent_grid(int items) {
     if (!g_sm_count) {
         int dev = 0;
@@ -497,6 +499,14 @@ int persistent_grid(int items) {
         if (cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sm_count < 1) g_sm_count = 148;
     }
     return items < g_sm_count ? items : g_sm_count;
+}
+
+int set_kernel_attributes() {
+    if (g_attr_set) return B2_OK;
+    B2_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    B2_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    g_attr_set = true;
+    return B2_OK;
 }
 
 }  // namespace
@@ -536,10 +546,8 @@ bool gemm_tc_supported(const SplitOperand &A, const SplitOperand &B, int m, int 
 int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, int m, int n, int k, bool accumulate, float *ws,
             size_t ws_floats, int *status, cudaStream_t st) {
     B2_TRY(get_encode());
-    if (!g_attr_set) {
-        B2_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        g_attr_set = true;
-    }
+    B2_TRY(set_kernel_attributes());
+    const int BN = n <= 64 ? 64 : 128;
     CUtensorMap mAh, mAl, mBh, mBl;
     if (A.kmajor) {
         B2_TRY(make_map(&mAh, A.hi, k, m, A.ld, BK, BM, true));
@@ -589,7 +597,10 @@ int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, in
     a.accumulate = accumulate ? 1 : 0; a.ws = ws; a.status = status;
     a.nbatch = 0; a.splits = splits; a.c_split_stride = 0; a.kseg_len = 0; a.kseg_stride = 0;
     a.tiles_m = (int)grid.x; a.tiles_n = (int)grid.y; a.nz = splits;
-    gemm_tf32x3_kernel<<<persistent_grid(a.tiles_m * a.tiles_n * a.nz), NTHREADS, SMEM_BYTES, st>>>(mAh, mAl, mBh, mBl, a);
+    if (BN == 64)
+        gemm_tf32x3_kernel<64><<<persistent_grid(a.tiles_m * a.tiles_n * a.nz), NTHREADS, SMEM_BYTES, st>>>(mAh, mAl, mBh, mBl, a);
+    else
+        gemm_tf32x3_kernel<128><<<persistent_grid(a.tiles_m * a.tiles_n * a.nz), NTHREADS, SMEM_BYTES, st>>>(mAh, mAl, mBh, mBl, a);
     count_launch();
     B2_CUDA(cudaGetLastError());
     if (splits > 1) {
@@ -606,6 +617,7 @@ int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, in
 // ---- planned, batched launches: the tensor maps are encoded once and reused for many launches that
 // differ only in coordinate offsets (one launch per timestep of the tensor-core recurrence)
 struct TcPlan {
+    int bn;   // N extent of the tile: 64 or 128
     CUtensorMap mAh, mAl, mBh, mBl;
     TcArgs args;
     dim3 grid;
@@ -614,10 +626,8 @@ struct TcPlan {
 int tc_plan_create(TcPlan **out, const SplitOperand &A, long a_inner, long a_outer, const SplitOperand &B, long b_inner,
                    long b_outer, int m, int n, int k, int splits, int kseg_len, int kseg_stride, long ldc) {
     B2_TRY(get_encode());
-    if (!g_attr_set) {
-        B2_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        g_attr_set = true;
-    }
+    B2_TRY(set_kernel_attributes());
+    const int BN = n <= 64 ? 64 : 128;
     // a segmented contraction index needs whole slabs per split; a contiguous one may be ragged (the
     // tensor maps fill the overhang with zeros as long as one operand's extent ends at k)
     if (splits < 1 || (kseg_len && ((k % (splits * BK)) != 0 || (kseg_len % BK) != 0))) {
@@ -625,6 +635,7 @@ int tc_plan_create(TcPlan **out, const SplitOperand &A, long a_inner, long a_out
         return B2_ERR_BAD_SHAPE;
     }
     TcPlan *p = new TcPlan;
+    p->bn = BN;
     int rc = make_map(&p->mAh, A.hi, a_inner, a_outer, A.ld, A.kmajor ? BK : 32, A.kmajor ? BM : BK, A.kmajor);
     if (rc == B2_OK) rc = make_map(&p->mAl, A.lo, a_inner, a_outer, A.ld, A.kmajor ? BK : 32, A.kmajor ? BM : BK, A.kmajor);
     if (rc == B2_OK) rc = make_map(&p->mBh, B.hi, b_inner, b_outer, B.ld, B.kmajor ? BK : 32, B.kmajor ? BN : BK, B.kmajor);
@@ -675,7 +686,10 @@ int tc_plan_launch(const TcPlan *p, float *C, const TcBatch *batches, int nbatch
         a.c_off[b] = batches[b].c_off;
     }
     a.tiles_m = (int)p->grid.x; a.tiles_n = (int)p->grid.y; a.nz = nbatch * a.splits;
-    gemm_tf32x3_kernel<<<persistent_grid(a.tiles_m * a.tiles_n * a.nz), NTHREADS, SMEM_BYTES, st>>>(p->mAh, p->mAl, p->mBh, p->mBl, a);
+    if (p->bn == 64)
+        gemm_tf32x3_kernel<64><<<persistent_grid(a.tiles_m * a.tiles_n * a.nz), NTHREADS, SMEM_BYTES, st>>>(p->mAh, p->mAl, p->mBh, p->mBl, a);
+    else
+        gemm_tf32x3_kernel<128><<<persistent_grid(a.tiles_m * a.tiles_n * a.nz), NTHREADS, SMEM_BYTES, st>>>(p->mAh, p->mAl, p->mBh, p->mBl, a);
     count_launch();
     B2_CUDA(cudaGetLastError());
     return B2_OK;
