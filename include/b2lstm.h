@@ -208,6 +208,13 @@ unsigned long long b2_net_launch_count(const b2_net *net);
 int b2_net_set_profiling(b2_net *net, int on);
 int b2_net_get_profile(b2_net *net, int cap, const char **names, float *ms, int *launches);
 
+/* Self-test of the failure path of the persistent kernels: one block waits, with the sweeps' own
+ * bounded wait, for a step tag that nothing writes.  The wait runs out after its budget (a second or
+ * two), the kernel records B2_ERR_STEP_TIMEOUT and returns; the context stays usable.  *status_out =
+ * the recorded code, *gave_up = 1 when the block left through the timeout path.  No counterpart in
+ * the reference (its kernels have no waits). */
+int b2_selftest_bounded_wait(int *status_out, int *gave_up);
+
 /* ------------------------------------------------------------------------------------------
  * Data-parallel training: sequences of a fraction are dealt to the ranks, every rank holds a
  * full weight replica, weightUpdates are summed with ncclAllReduce before the update.

@@ -75,6 +75,7 @@ SIGNATURES = {
     "b2_net_launch_count": (C.c_ulonglong, [C.c_void_p]),
     "b2_net_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_net_get_profile": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_char_p), _fp, _ip]),
+    "b2_selftest_bounded_wait": (C.c_int, [_ip, _ip]),
     "b2_dp_get_unique_id": (C.c_int, [C.c_void_p]),
     "b2_dp_attach": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "b2_dp_detach": (C.c_int, [C.c_void_p]),
@@ -193,6 +194,13 @@ class LstmLayer:
     @property
     def state_bytes(self):
         return int(lib().b2_lstm_state_bytes(self.h))
+
+
+def selftest_bounded_wait():
+    """(recorded status, left through the timeout path): see b2_selftest_bounded_wait"""
+    st, gu = C.c_int(), C.c_int()
+    _check(lib().b2_selftest_bounded_wait(C.byref(st), C.byref(gu)))
+    return st.value, bool(gu.value)
 
 
 def dp_unique_id():

@@ -164,6 +164,8 @@ int persistent_ps(int els, int P, int D, bool use_cluster);   // sequences per w
 int lstm_persistent(bool backward, bool use_cluster, const LstmShape &s, const LstmBuffers &b, const float *w, float *y,
                     const float *dy, unsigned long long *xchg, int *status, unsigned *tag_next, cudaStream_t st);
 
+int lstm_selftest_bounded_wait(int *status_out, int *gave_up, cudaStream_t st);
+
 // offsets inside the (b)lstm weight vector
 struct LstmOffsets {
     size_t bias, rec, peep, total;

@@ -304,6 +304,11 @@ struct b2_lstm {
 
 extern "C" {
 
+int b2_selftest_bounded_wait(int *status_out, int *gave_up) {
+    return b2::lstm_selftest_bounded_wait(status_out, gave_up, nullptr);
+}
+
+
 size_t b2_lstm_num_weights(const b2_lstm_desc *d) {
     if (!d) return 0;
     size_t ls = d->size, pls = d->prev_size, els = d->bidirectional ? ls / 2 : ls;

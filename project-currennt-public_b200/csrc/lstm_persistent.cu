@@ -102,6 +102,16 @@ __device__ __forceinline__ void gather_pairs(float (&v)[(COUNT + NT - 1) / NT], 
     for (int q = 0; q < NW; ++q) v[q] = ((unsigned)(x[q] >> 32) == tag) ? __uint_as_float((unsigned)x[q]) : 0.0f;
 }
 
+// One block waits, with the sweeps' own gather, for a tag that nothing writes: the wait must run out, record
+// B2_ERR_STEP_TIMEOUT and return (see lstm_selftest_bounded_wait).
+__global__ void __launch_bounds__(NT) bounded_wait_selftest_kernel(const u64 *xb, int *status, float *out) {
+    float v[1];
+    int gave_up = 0;
+    gather_pairs<NT>(v, xb, 0x5EEDu, (int)threadIdx.x, &gave_up, status);
+    const int any = __syncthreads_or(gave_up);
+    if (threadIdx.x == 0) out[0] = any ? 1.0f : 0.0f;
+}
+
 // ---- thread-block cluster exchange
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
@@ -747,6 +757,33 @@ size_t lstm_persistent_xchg_words(int els, int P, int D) {
     if (max_slots < 1) max_slots = 1;
     size_t fwd = (size_t)4 * els * PS, bwd = (size_t)4 * G * G * JB * PS;
     return (size_t)max_slots * (fwd > bwd ? fwd : bwd);
+}
+
+// Runs the bounded wait of the sweeps on a word whose tag never arrives.  *status_out receives what the
+// kernel recorded (B2_ERR_STEP_TIMEOUT expected), *gave_up whether the block left through the timeout
+// path.  Takes about as long as the wait budget (a second or two); the context stays usable.
+int lstm_selftest_bounded_wait(int *status_out, int *gave_up, cudaStream_t st) {
+    u64 *xb = nullptr;
+    int *status = nullptr;
+    float *out = nullptr;
+    B2_CUDA(cudaMalloc(&xb, NT * sizeof(u64)));
+    B2_CUDA(cudaMalloc(&status, sizeof(int)));
+    B2_CUDA(cudaMalloc(&out, sizeof(float)));
+    B2_CUDA(cudaMemsetAsync(xb, 0, NT * sizeof(u64), st));
+    B2_CUDA(cudaMemsetAsync(status, 0, sizeof(int), st));
+    B2_CUDA(cudaMemsetAsync(out, 0, sizeof(float), st));
+    bounded_wait_selftest_kernel<<<1, NT, 0, st>>>(xb, status, out);
+    count_launch();
+    int hs = 0;
+    float ho = 0.0f;
+    cudaError_t e = cudaMemcpyAsync(&hs, status, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&ho, out, sizeof(float), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(xb); cudaFree(status); cudaFree(out);
+    B2_CUDA(e);
+    if (status_out) *status_out = hs;
+    if (gave_up) *gave_up = ho != 0.0f ? 1 : 0;
+    return B2_OK;
 }
 
 // returns B2_OK, an error, or 1 when this shape has no persistent kernel (caller uses the stepwise one)

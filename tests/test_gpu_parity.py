@@ -314,3 +314,24 @@ def test_errors_are_status_codes():
     with pytest.raises(b2lstm.B2Error):
         net.load_fraction(np.array([9], np.int32), np.zeros((9, 2, 4), np.float32), np.zeros((9, 2, 4), np.float32))
     net.close()
+
+
+def test_a_wait_that_nothing_satisfies_runs_out_and_leaves_the_context_usable():
+    """The failure path of the persistent kernels without any fault: a block waits, with the sweeps' own
+    bounded wait, for a step tag that nothing writes.  The wait runs out, the kernel records
+    B2_ERR_STEP_TIMEOUT and returns; afterwards the same context trains a step with correct results."""
+    import time
+    import b2lstm
+    from b2lstm import workloads
+    from b2lstm.lib import selftest_bounded_wait
+    t0 = time.time()
+    status, gave_up = selftest_bounded_wait()
+    assert status == -3 and gave_up                 # B2_ERR_STEP_TIMEOUT
+    assert time.time() - t0 < 30.0
+    layers = L(("input", 6), ("blstm", 256), ("feedforward_identity", 3), ("sse", 3))
+    lens = np.array([9, 7, 9, 4], np.int32)
+    x, tg = workloads.make_fraction(6, 3, 4, lens, 11, 12)
+    w = workloads.make_weights(layers, 13, 0.1)
+    want = run_kind(checker(), layers, 4, lens, x, tg, w)
+    got = run_gpu(layers, 4, lens, x, tg, w, VARIANTS[2])
+    parity.compare_run(layers, got, want, "after the timed-out wait", lstm_pad_zero_lens=lens)
