@@ -112,10 +112,32 @@ int FeedForwardLayer::computeBackwardPass(int) {
         ProfScope ps(net_, "ff_backward_gemm");
         // dX(pls x N) = W delta, overwrite (assignProduct, FeedForwardLayer.cu:1690); nobody reads the
         // errors of an input layer, so that product is skipped
-        if (prev_->precedingLayer())
-            B2_TRY(net_.gemm(prev_->outputErrors(), pls, weights_, 1, pls, outputErrors_, 1, ls, pls, N, ls, false));
-        // dW(pls x ls) = X delta^T (FeedForwardLayer.cu:1719)
-        B2_TRY(net_.gemm(weightUpdates_, pls, prev_->outputs(), 1, pls, outputErrors_, ls, 1, pls, ls, N, false));
+        const bool wantDx = prev_->precedingLayer() != nullptr;
+        const bool tc = !net_.forceFfma && gemm_wants_tc(1, pls, ls, 1, pls, ls, N) &&
+                        (!wantDx || gemm_wants_tc(1, pls, 1, ls, pls, N, ls));
+        if (tc) {
+            // both products on the tensor cores: the deltas are split into tf32 hi/lo parts ONCE; the same
+            // [frame][unit] copy serves as the K-major operand of dX and as the MN-major operand of dW
+            TcScratch &sc = net_.tcScratch;
+            B2_TRY(sc.reserve(split_floats(N, ls) + split_floats(N, pls) + split_floats(ls, pls)));
+            sc.used = 0;
+            SplitOperand sD{}, sX{}, sW{};
+            B2_TRY(split_operand(sc, outputErrors_, ls, N, ls, true, &sD, net_.stream));
+            if (wantDx) {
+                B2_TRY(split_operand(sc, weights_, pls, ls, pls, false, &sW, net_.stream));
+                B2_TRY(gemm_tc(prev_->outputErrors(), pls, sW, sD, pls, N, ls, false, net_.ws, net_.wsFloats, net_.statusDev,
+                               net_.stream));
+            }
+            B2_TRY(split_operand(sc, prev_->outputs(), pls, N, pls, false, &sX, net_.stream));
+            SplitOperand sDt = sD;
+            sDt.kmajor = false;
+            B2_TRY(gemm_tc(weightUpdates_, pls, sX, sDt, pls, ls, N, false, net_.ws, net_.wsFloats, net_.statusDev, net_.stream));
+        } else {
+            if (wantDx)
+                B2_TRY(net_.gemm(prev_->outputErrors(), pls, weights_, 1, pls, outputErrors_, 1, ls, pls, N, ls, false));
+            // dW(pls x ls) = X delta^T (FeedForwardLayer.cu:1719)
+            B2_TRY(net_.gemm(weightUpdates_, pls, prev_->outputs(), 1, pls, outputErrors_, ls, 1, pls, ls, N, false));
+        }
     }
     ProfScope ps(net_, "ff_bias_grad");
     // bias gradient = bias * sum over frames of delta (FeedForwardLayer.cu:118-138,1517-1533)
