@@ -169,6 +169,17 @@ int b2_net_backward(b2_net *net);
  * (SteepestDescentOptimizer.cu:425-426).  With a data-parallel communicator attached the
  * gradients are first summed over all ranks. */
 int b2_net_update_weights(b2_net *net, float learning_rate, float momentum);
+/* The optimizer option of the reference (--optimizer; MacroDefine.hpp:32-37; gradient shaping in
+ * SteepestDescentOptimizer::_updateWeights, SteepestDescentOptimizer.cu:127-194,306-395) applied by
+ * every later update: 0 plain steepest descent (default), 1 AdaGrad, 2 gradient averaged over the
+ * fraction's frames, 3 steepest descent that accumulates the AdaGrad statistics, 5 Adam
+ * (beta1 0.9, beta2 0.999, epsilon 1e-8).  Setting it (re)initialises the statistics as the
+ * reference's Optimizer constructor does (Optimizer.cu:421-457).  With a data-parallel communicator
+ * attached the frame count is summed over the ranks. */
+int b2_net_set_optimizer(b2_net *net, int option);
+/* Optimizer::m_weightStats of one layer (AdaGrad: one float per weight; Adam: m and v interleaved),
+ * the "optimizer_status_vector" of an autosave.  host_out may be NULL to ask for *count only. */
+int b2_net_get_optimizer_stats(b2_net *net, int layer, float *host_out, size_t capacity, size_t *count);
 /* One iteration of the minibatch loop of Optimizer::_processDataSet (Optimizer.cu:68-231) with
  * hybrid_online_batch: load, forward, error, backward, [all-reduce], update.  *error may be NULL. */
 int b2_net_train_step(b2_net *net, int T, int n_seqs, const int *seq_lens, const float *host_inputs,

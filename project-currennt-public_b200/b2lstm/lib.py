@@ -59,6 +59,8 @@ SIGNATURES = {
     "b2_net_forward": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
     "b2_net_backward": (C.c_int, [C.c_void_p]),
     "b2_net_update_weights": (C.c_int, [C.c_void_p, C.c_float, C.c_float]),
+    "b2_net_set_optimizer": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2_net_get_optimizer_stats": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
     "b2_net_train_step": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float,
                                     C.c_float, C.POINTER(C.c_double)]),
     "b2_net_prefetch_fraction": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -351,6 +353,18 @@ class Net:
         ln = (C.c_int * cap)()
         n = lib().b2_net_get_profile(self.h, cap, names, ms, ln)
         return {names[i].decode(): (float(ms[i]), int(ln[i])) for i in range(n)}
+
+    def set_optimizer(self, option):
+        """0 plain, 1 AdaGrad, 2 average gradient, 3 SGD accumulating AdaGrad statistics, 5 Adam"""
+        _check(lib().b2_net_set_optimizer(self.h, option))
+
+    def optimizer_stats(self, i):
+        n = C.c_size_t()
+        _check(lib().b2_net_get_optimizer_stats(self.h, i, None, 0, C.byref(n)))
+        out = np.empty(n.value, np.float32)
+        if n.value:
+            _check(lib().b2_net_get_optimizer_stats(self.h, i, out.ctypes.data, n.value, None))
+        return out
 
     def export_json(self, digits=0):
         """The network as the reference's network.jsn text (layers + weights)."""

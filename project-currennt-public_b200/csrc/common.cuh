@@ -113,6 +113,11 @@ int sse_loss(double *loss_dev, const float *y, const float *tgt, const char *pat
 int sse_grad(float *dy, const float *y, const float *tgt, const char *pat, int ls, size_t frames, cudaStream_t st);
 // steepest descent with momentum; zeroes NaN/Inf gradient entries first
 int sgd_update(float *w, float *g, float *delta, size_t n, float lr, float mom, cudaStream_t st);
+// the same after shaping the gradient: option 1 AdaGrad, 2 average over *frac_len_dev frames, 3 plain SGD that
+// accumulates the AdaGrad statistics, 5 Adam; stats holds n floats (2n for Adam)
+int sgd_update_opt(float *w, float *g, float *delta, float *stats, size_t n, float lr, float mom, int option,
+                   const float *frac_len_dev, float beta1_accum, float beta2_accum, cudaStream_t st);
+int fill_value(float *p, size_t n, float v, cudaStream_t st);
 int fill_zero(void *p, size_t bytes, cudaStream_t st);
 
 // ---- LSTM recurrence (lstm_step.cu, lstm_persistent.cu) -------------------------------------------

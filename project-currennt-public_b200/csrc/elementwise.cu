@@ -131,6 +131,41 @@ __global__ void sgd_update_kernel(float *__restrict__ w, float *__restrict__ g, 
     }
 }
 
+// Gradient shaping of SteepestDescentOptimizer::_updateWeights (SteepestDescentOptimizer.cu:127-194,
+// 306-395) fused with the update functor: option 1 AdaGrad, 2 average over the fraction's frames,
+// 3 SGD that only accumulates the AdaGrad statistics, 5 Adam (constants of MacroDefine.hpp:39-42).
+__global__ void sgd_update_opt_kernel(float *__restrict__ w, float *__restrict__ g, float *__restrict__ delta,
+                                      float *__restrict__ stats, size_t n, float lr, float mom, int option,
+                                      const float *__restrict__ frac_len, float beta1_accum, float beta2_accum) {
+    const float fracLength = *frac_len;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float gi = g[i];
+        if (isnan(gi) || isinf(gi)) { gi = 0.0f; g[i] = 0.0f; }
+        const float ave = gi / fracLength;
+        if (option == 2) {
+            gi = ave;
+        } else if (option == 1 || option == 3) {
+            const float st = stats[i] + ave * ave;
+            stats[i] = st;
+            if (option == 1) gi = ave / sqrtf(st);
+        } else if (option == 5) {
+            const float m = stats[2 * i] * 0.9f + ave * (1.0f - 0.9f);
+            const float v = stats[2 * i + 1] * 0.999f + ave * ave * (1.0f - 0.999f);
+            stats[2 * i] = m;
+            stats[2 * i + 1] = v;
+            gi = (m / (1.0f - beta1_accum)) / (sqrtf(v / (1.0f - beta2_accum)) + 0.00000001f);
+        }
+        float dl = mom * delta[i] - lr * gi;
+        delta[i] = dl;
+        w[i] = w[i] + dl;
+    }
+}
+__global__ void fill_value_kernel(float *p, size_t n, float v) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = v;
+}
+
 inline int grid_for(size_t n, int threads, int per_sm = 8) {
     size_t b = (n + threads - 1) / threads;
     size_t cap = (size_t)SMS * per_sm;
@@ -206,6 +241,24 @@ int sse_grad(float *dy, const float *y, const float *tgt, const char *pat, int l
 int sgd_update(float *w, float *g, float *delta, size_t n, float lr, float mom, cudaStream_t st) {
     if (!n) return B2_OK;
     sgd_update_kernel<<<grid_for(n, 256), 256, 0, st>>>(w, g, delta, n, lr, mom);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int sgd_update_opt(float *w, float *g, float *delta, float *stats, size_t n, float lr, float mom, int option,
+                   const float *frac_len_dev, float beta1_accum, float beta2_accum, cudaStream_t st) {
+    if (!n) return B2_OK;
+    sgd_update_opt_kernel<<<grid_for(n, 256), 256, 0, st>>>(w, g, delta, stats, n, lr, mom, option, frac_len_dev, beta1_accum,
+                                                         beta2_accum);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int fill_value(float *p, size_t n, float v, cudaStream_t st) {
+    if (!n) return B2_OK;
+    fill_value_kernel<<<grid_for(n, 256), 256, 0, st>>>(p, n, v);
     count_launch();
     B2_CUDA(cudaGetLastError());
     return B2_OK;

@@ -67,6 +67,7 @@ TrainableLayer::~TrainableLayer() {
     cudaFree(weights_);
     cudaFree(weightUpdates_);
     cudaFree(weightDeltas_);
+    cudaFree(weightStats_);
 }
 int TrainableLayer::allocateWeights(size_t n) {
     nW_ = n;
@@ -77,6 +78,15 @@ int TrainableLayer::allocateWeights(size_t n) {
     B2_CUDA(cudaMemset(weightUpdates_, 0, n * sizeof(float)));
     B2_CUDA(cudaMemset(weightDeltas_, 0, n * sizeof(float)));
     return B2_OK;
+}
+
+int TrainableLayer::allocateStats(size_t floats, float init, cudaStream_t st) {
+    if (weightStats_ && statsFloats_ == floats) return fill_value(weightStats_, floats, init, st);
+    if (weightStats_) { B2_CUDA(cudaStreamSynchronize(st)); cudaFree(weightStats_); weightStats_ = nullptr; }
+    statsFloats_ = floats;
+    if (!floats) return B2_OK;
+    B2_CUDA(cudaMalloc(&weightStats_, floats * sizeof(float)));
+    return fill_value(weightStats_, floats, init, st);
 }
 
 // ---- InputLayer (layers/InputLayer.cu:162-164): outputs = the fraction's inputs ------------------------
@@ -218,7 +228,7 @@ int SsePostOutputLayer::computeBackwardPass(int) {
 NeuralNetwork::~NeuralNetwork() {
     if (dp) dp_detach(*this);
     layers.clear();
-    cudaFree(ws); cudaFree(statusDev);
+    cudaFree(ws); cudaFree(statusDev); cudaFree(fracLenDev);
     for (int b = 0; b < 2; ++b) {
         cudaFree(inBuf[b]); cudaFree(tgBuf[b]); cudaFree(patBuf[b]);
         if (patPinned[b]) cudaFreeHost(patPinned[b]);
@@ -446,13 +456,46 @@ int NeuralNetwork::computeBackwardPass() {
     }
     return B2_OK;
 }
+// Optimizer constructor, option part (optimizers/Optimizer.cu:421-457): AdaGrad statistics start at
+// OP_ADAGRADFACTOR, Adam's first and second moments at zero
+int NeuralNetwork::setOptimizerOption(int option) {
+    if (option != 0 && option != 1 && option != 2 && option != 3 && option != 5) {
+        set_error("b2_net_set_optimizer: option %d (0 plain, 1 AdaGrad, 2 average gradient, 3 SGD+AdaGrad statistics, 5 Adam)", option);
+        return B2_ERR_BAD_ARG;
+    }
+    optOption = option;
+    adamBeta1Accum = adamBeta2Accum = 1.0f;
+    if (!fracLenDev) B2_CUDA(cudaMalloc(&fracLenDev, sizeof(float)));
+    for (size_t i = 0; i < layers.size(); ++i) {
+        TrainableLayer *t = dynamic_cast<TrainableLayer *>(layers[i].get());
+        if (!t) continue;
+        if (option == 1 || option == 3) B2_TRY(t->allocateStats(t->numWeights(), 0.000001f, stream));
+        else if (option == 5) B2_TRY(t->allocateStats(2 * t->numWeights(), 0.0f, stream));
+        else B2_TRY(t->allocateStats(0, 0.0f, stream));
+    }
+    return B2_OK;
+}
+
 int NeuralNetwork::updateWeights(float lr, float mom) {
     ProfScope ps(*this, "sgd_update");
+    if (optOption > 0) {
+        // frames of the fraction (summed over the ranks of a data-parallel job): the gradient is averaged over them
+        B2_TRY(fill_value(fracLenDev, 1, (float)frac.realFrames, stream));
+        if (dp) B2_TRY(dp_allreduce_sum(*this, fracLenDev, 1, stream));
+        if (optOption == 5) {   // SteepestDescentOptimizer.cu:339-343
+            adamBeta1Accum *= 0.9f;
+            adamBeta2Accum *= 0.999f;
+        }
+    }
     for (size_t i = 0; i < layers.size(); ++i) {
         TrainableLayer *t = dynamic_cast<TrainableLayer *>(layers[i].get());
         if (!t) continue;
         float rate = t->learningRate() >= 0.0f ? t->learningRate() : lr;  // SteepestDescentOptimizer.cu:425-426
-        B2_TRY(sgd_update(t->weights(), t->weightUpdates(), t->weightDeltas(), t->numWeights(), rate, mom, stream));
+        if (optOption > 0)
+            B2_TRY(sgd_update_opt(t->weights(), t->weightUpdates(), t->weightDeltas(), t->weightStats(), t->numWeights(), rate, mom,
+                                  optOption, fracLenDev, adamBeta1Accum, adamBeta2Accum, stream));
+        else
+            B2_TRY(sgd_update(t->weights(), t->weightUpdates(), t->weightDeltas(), t->numWeights(), rate, mom, stream));
     }
     return B2_OK;
 }
@@ -606,6 +649,18 @@ int b2_net_forward(b2_net *n, double *error) {
 }
 int b2_net_backward(b2_net *n) { return n ? n->net.computeBackwardPass() : B2_ERR_BAD_ARG; }
 int b2_net_update_weights(b2_net *n, float lr, float mom) { return n ? n->net.updateWeights(lr, mom) : B2_ERR_BAD_ARG; }
+int b2_net_set_optimizer(b2_net *n, int option) { return n ? n->net.setOptimizerOption(option) : B2_ERR_BAD_ARG; }
+int b2_net_get_optimizer_stats(b2_net *n, int i, float *host, size_t capacity, size_t *count) {
+    TrainableLayer *t = trainable(n, i);
+    if (!t) { set_error("b2_net_get_optimizer_stats: layer %d has no weights", i); return B2_ERR_BAD_ARG; }
+    if (count) *count = t->statsFloats();
+    if (host) {
+        if (capacity < t->statsFloats()) { set_error("b2_net_get_optimizer_stats: %zu floats needed", t->statsFloats()); return B2_ERR_BAD_SHAPE; }
+        B2_CUDA(cudaMemcpyAsync(host, t->weightStats(), t->statsFloats() * sizeof(float), cudaMemcpyDeviceToHost, n->net.stream));
+        B2_CUDA(cudaStreamSynchronize(n->net.stream));
+    }
+    return B2_OK;
+}
 
 int b2_net_train_step(b2_net *n, int T, int nSeq, const int *lens, const float *in, const float *tg, float lr,
                       float mom, double *error) {

@@ -66,6 +66,10 @@ public:
     float *weights() { return weights_; }
     float *weightUpdates() { return weightUpdates_; }
     float *weightDeltas() { return weightDeltas_; }
+    float *weightStats() { return weightStats_; }
+    size_t statsFloats() const { return statsFloats_; }
+    // AdaGrad / Adam statistics (Optimizer::m_weightStats): n floats filled with `init`, or 2n zeros for Adam
+    int allocateStats(size_t floats, float init, cudaStream_t st);
     float bias() const { return bias_; }
     float learningRate() const { return learningRate_; }
     int allocateWeights(size_t n);
@@ -73,7 +77,8 @@ public:
 protected:
     size_t nW_ = 0;
     float bias_, learningRate_;
-    float *weights_ = nullptr, *weightUpdates_ = nullptr, *weightDeltas_ = nullptr;
+    float *weights_ = nullptr, *weightUpdates_ = nullptr, *weightDeltas_ = nullptr, *weightStats_ = nullptr;
+    size_t statsFloats_ = 0;
 };
 
 class InputLayer : public Layer {
@@ -143,6 +148,12 @@ public:
     int calculateError(double *hostError);
     int computeBackwardPass();
     int updateWeights(float lr, float mom);
+    // optimizer option of the reference (MacroDefine.hpp:32-37): 0 plain, 1 AdaGrad, 2 average gradient,
+    // 3 SGD accumulating AdaGrad statistics, 5 Adam
+    int setOptimizerOption(int option);
+    int optOption = 0;
+    float adamBeta1Accum = 1.0f, adamBeta2Accum = 1.0f;
+    float *fracLenDev = nullptr;
     int synchronize();
 
     std::vector<std::unique_ptr<Layer> > layers;

@@ -374,8 +374,19 @@ int b2_optimizer_save_state(b2_optimizer *o, const char *filename, const char *c
         out += "\":";
         put_number(out, n.v, digits);
     }
-    out += ",\n\"optimizer_status\":0";   // plain steepest descent (MacroDefine.hpp OPTIMIZATION_*)
+    out += ",\n\"optimizer_status\":" + std::to_string(nn.optOption);   // MacroDefine.hpp OPTIMIZATION_*
     put_per_layer(out, "optimizer_best_weights", o->bestWeights, digits);
+    if (nn.optOption == 1 || nn.optOption == 3 || nn.optOption == 5) {
+        // AdaGrad / Adam statistics (Optimizer.cu:721-725); Adam's running beta products are not part of the
+        // reference's file either and restart at 1 after a continue
+        std::vector<std::vector<float> > stats(nn.layers.size());
+        for (size_t i = 1; i < nn.layers.size(); ++i)
+            if (TrainableLayer *t = dynamic_cast<TrainableLayer *>(nn.layers[i].get())) {
+                stats[i].resize(t->statsFloats());
+                if (!stats[i].empty()) B2_TRY(b2_net_get_optimizer_stats(o->net, (int)i, stats[i].data(), stats[i].size(), nullptr));
+            }
+        put_per_layer(out, "optimizer_status_vector", stats, digits);
+    }
     if (o->opt.momentum > 0.0f) {
         std::vector<std::vector<float> > deltas(nn.layers.size());
         for (size_t i = 1; i < nn.layers.size(); ++i)
@@ -438,8 +449,31 @@ int b2_optimizer_restore_state(b2_optimizer *o, const char *filename, char *info
     const float va = (float)checked_number(doc, "optimizer_cur_validation_error", &ok);
     const float te = (float)checked_number(doc, "optimizer_cur_test_error", &ok);
     if (!ok) return B2_ERR_BAD_ARG;
+    const int option = (int)checked_number(doc, "optimizer_status", &ok);
+    if (!ok) return B2_ERR_BAD_ARG;
     std::vector<std::vector<float> > best, deltas;
     B2_TRY(per_layer_vectors(doc, "optimizer_best_weights", nn, &best));
+    B2_TRY(nn.setOptimizerOption(option));
+    if (option == 1 || option == 3 || option == 5) {
+        const json::Value *a = doc.find("optimizer_status_vector");
+        if (!a || a->kind != json::Value::Array || a->arr.size() != nn.layers.size()) {
+            set_error("Array 'optimizer_status_vector' is missing or has the wrong type");
+            return B2_ERR_BAD_ARG;
+        }
+        for (size_t i = 1; i < nn.layers.size(); ++i) {
+            TrainableLayer *t = dynamic_cast<TrainableLayer *>(nn.layers[i].get());
+            if (!t) continue;
+            const json::Value &v = a->arr[i];
+            if (v.kind != json::Value::Array || v.arr.size() != t->statsFloats()) {
+                set_error("Subarray in 'optimizer_status_vector' has a wrong size");
+                return B2_ERR_BAD_SHAPE;
+            }
+            std::vector<float> h(v.arr.size());
+            for (size_t k = 0; k < h.size(); ++k) h[k] = (float)v.arr[k].num;
+            B2_CUDA(cudaMemcpyAsync(t->weightStats(), h.data(), h.size() * sizeof(float), cudaMemcpyHostToDevice, nn.stream));
+            B2_CUDA(cudaStreamSynchronize(nn.stream));
+        }
+    }
     if (o->opt.momentum > 0.0f) {
         B2_TRY(per_layer_vectors(doc, "steepest_descent_optimizer_weight_deltas", nn, &deltas));
         for (size_t i = 1; i < nn.layers.size(); ++i)

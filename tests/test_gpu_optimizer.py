@@ -124,3 +124,59 @@ def test_training_run_stops_on_validation_error_and_restores_best_weights(tmp_pa
         o.close()
     for n in (net, net_a, net_b):
         n.close()
+
+
+@pytest.mark.parametrize("option", [1, 2, 3, 5])
+def test_optimizer_options_follow_the_reference_formulas(option):
+    """AdaGrad (1), averaged gradient (2), SGD accumulating AdaGrad statistics (3) and Adam (5): three
+    updates on different fractions against a float32 numpy restatement of the reference's functors
+    (optimizers/SteepestDescentOptimizer.cu:127-194 with the constants of MacroDefine.hpp:39-42), fed
+    with the gradients the GPU produced."""
+    import b2lstm
+    from b2lstm import workloads
+    layers = L(("input", 5), ("blstm", 12), ("feedforward_identity", 3), ("sse", 3))
+    P = 3
+    w0 = workloads.make_weights(layers, 21, 0.2)
+    net = b2lstm.Net(layers, P, 12)
+    for i, wi in w0.items():
+        net.set_weights(i, wi)
+    net.set_optimizer(option)
+    f32 = np.float32
+    lr, mom = f32(1e-2), f32(0.9)
+    w = {i: wi.copy() for i, wi in w0.items()}
+    delta = {i: np.zeros_like(wi) for i, wi in w0.items()}
+    stats = {i: (np.zeros(2 * wi.size, f32) if option == 5 else np.full(wi.size, 1e-6, f32)) for i, wi in w0.items()}
+    b1 = b2 = f32(1.0)
+    for k, lens in enumerate([[12, 9, 4], [7, 7, 7], [10, 2]]):
+        lens = np.array(lens, np.int32)
+        x, tg = workloads.make_fraction(5, 3, P, lens, 30 + k, 40 + k)
+        net.load_fraction(lens, x, tg)
+        net.forward()
+        net.backward()
+        g = {i: net.weight_updates(i) for i in w0}
+        net.update_weights(float(lr), float(mom))
+        n = f32(lens.sum())
+        if option == 5:
+            b1, b2 = f32(b1 * f32(0.9)), f32(b2 * f32(0.999))
+        for i in w0:
+            ave = (g[i] / n).astype(f32)
+            if option == 2:
+                gi = ave
+            elif option in (1, 3):
+                stats[i] = (stats[i] + ave * ave).astype(f32)
+                gi = (ave / np.sqrt(stats[i])).astype(f32) if option == 1 else g[i]
+            else:
+                m = (stats[i][0::2] * f32(0.9) + ave * (f32(1.0) - f32(0.9))).astype(f32)
+                v = (stats[i][1::2] * f32(0.999) + ave * ave * (f32(1.0) - f32(0.999))).astype(f32)
+                stats[i][0::2], stats[i][1::2] = m, v
+                gi = ((m / (f32(1.0) - b1)) / (np.sqrt(v / (f32(1.0) - b2)) + f32(1e-8))).astype(f32)
+            delta[i] = (mom * delta[i] - lr * gi).astype(f32)
+            w[i] = (w[i] + delta[i]).astype(f32)
+            got = net.get_weights(i)
+            assert np.allclose(got, w[i], rtol=2e-5, atol=1e-7), (option, k, i, np.abs(got - w[i]).max())
+            assert np.allclose(net.optimizer_stats(i), stats[i], rtol=2e-5, atol=1e-12)
+            w[i] = got                       # follow the device weights: the next gradients come from them
+            net.set_weight_deltas(i, delta[i])
+    net.set_optimizer(0)
+    assert net.optimizer_stats(1).size == 0
+    net.close()
