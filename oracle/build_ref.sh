@@ -3,7 +3,7 @@
 # LSTM training path into oracle/_ref/libcurrennt_ref.so (serial Thrust host backend, the
 # reference's CMake default) and oracle/_ref/libcurrennt_ref_omp.so (Thrust OpenMP host backend).
 #
-# The sources are compiled from the reference checkout ($REF, default /root/reference); nothing
+# The sources are compiled from the reference checkout (the directory in $REF); nothing
 # of them is kept: one mechanical rewrite is needed for CUDA 12.9 (Thrust 2.8 maps thrust::tuple
 # onto cuda::std::tuple, which has no .get<N>() member, so `x.get<N>()` becomes
 # `thrust::get<N>(x)`), it is applied to a scratch copy under oracle/_ref/build/ that is deleted
