@@ -238,6 +238,11 @@ int b2_dp_attach(b2_net *net, int rank, int world_size, const void *id_bytes);
 int b2_dp_detach(b2_net *net);
 /* Sum a double over all ranks (loss / frame counts). Synchronises. */
 int b2_dp_allreduce_scalar(b2_net *net, double *value);
+/* Number of ranks of the attached communicator; 1 when none is attached. */
+int b2_dp_world_size(const b2_net *net);
+/* The train step of a rank that has NO sequence in the current fraction (a sharded data set near the
+ * end of an epoch): zero gradients go into the all-reduce, the update runs as on the other ranks. */
+int b2_net_train_step_empty(b2_net *net, float learning_rate, float momentum);
 
 /* ------------------------------------------------------------------------------------------
  * Data sets: the toolkit's .nc files (netCDF classic; CURRENNT_codes/README section 5) read
@@ -256,6 +261,12 @@ typedef struct {
     unsigned random_seed;     /* --random_seed: seeds the process-wide shuffle generator at its first use */
     int training_mode;        /* non-zero: segments are sorted by length (DataSet.cpp:1898-1900) */
     int loader_threads;       /* threads that convert one fraction; 0 = min(8, hardware threads) */
+    /* Data-parallel sharding (no counterpart in the reference): with shard_count = S > 1 a fraction spans
+     * parallel_sequences * S sequences, dealt to the shards in snake order (0 1 .. S-1, S-1 .. 1 0, ...)
+     * so that frames and longest lengths balance; this handle assembles shard_rank's sequences only, padded
+     * to that shard's own longest sequence.  At the end of an epoch a shard's fraction may be empty
+     * (num_sequences 0).  shard_count 0 means 1. */
+    int shard_rank, shard_count;
 } b2_data_options;
 
 typedef struct {

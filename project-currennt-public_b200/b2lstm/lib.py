@@ -82,6 +82,8 @@ SIGNATURES = {
     "b2_dp_attach": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "b2_dp_detach": (C.c_int, [C.c_void_p]),
     "b2_dp_allreduce_scalar": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
+    "b2_dp_world_size": (C.c_int, [C.c_void_p]),
+    "b2_net_train_step_empty": (C.c_int, [C.c_void_p, C.c_float, C.c_float]),
     "b2_data_open": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_char_p), C.c_int, C.c_void_p]),
     "b2_data_close": (None, [C.c_void_p]),
     "b2_data_info": (C.c_int, [C.c_void_p, _ip, C.POINTER(C.c_longlong), _ip, _ip, _ip, _ip]),
@@ -401,7 +403,7 @@ class Net:
 class _DataOptions(C.Structure):
     _fields_ = [("parallel_sequences", C.c_int), ("fraction", C.c_float), ("trunc_seq_length", C.c_int),
                 ("fraction_shuffling", C.c_int), ("sequence_shuffling", C.c_int), ("random_seed", C.c_uint),
-                ("training_mode", C.c_int), ("loader_threads", C.c_int)]
+                ("training_mode", C.c_int), ("loader_threads", C.c_int), ("shard_rank", C.c_int), ("shard_count", C.c_int)]
 
 
 class _Fraction(C.Structure):
@@ -416,12 +418,13 @@ class DataSet:
     fractions."""
 
     def __init__(self, paths, parallel_sequences, fraction=1.0, trunc_seq_length=0, fraction_shuffling=False,
-                 sequence_shuffling=False, random_seed=0, training_mode=True, loader_threads=0):
+                 sequence_shuffling=False, random_seed=0, training_mode=True, loader_threads=0, shard_rank=0,
+                 shard_count=1):
         if isinstance(paths, str):
             paths = [paths]
         arr = (C.c_char_p * len(paths))(*[os.fsencode(p) for p in paths])
         opt = _DataOptions(parallel_sequences, fraction, trunc_seq_length, int(fraction_shuffling),
-                           int(sequence_shuffling), random_seed, int(training_mode), loader_threads)
+                           int(sequence_shuffling), random_seed, int(training_mode), loader_threads, shard_rank, shard_count)
         self.h = C.c_void_p()
         _check(lib().b2_data_open(C.byref(self.h), arr, len(paths), C.byref(opt)))
         self.P = parallel_sequences
@@ -457,6 +460,11 @@ class DataSet:
             return None
         _check(rc)
         T, P, n = f.max_seq_length, self.P, f.num_sequences
+        if n == 0:      # a shard without sequences in this fraction
+            return {"T": 0, "min_seq_length": 0, "num_sequences": 0, "total_frames": 0, "seq_lengths": np.zeros(0, np.int32),
+                    "inputs": np.zeros((0, P, self.input_size), np.float32),
+                    "targets": np.zeros((0, P, self.output_size), np.float32), "pat_types": np.zeros((0, P), np.int8),
+                    "tags": [], "original_seq_idx": []}
         tags, orig = [], []
         buf = C.create_string_buffer(1024)
         k = C.c_int()

@@ -43,6 +43,8 @@ int b2_data_open(b2_data **out, const char *const *nc_paths, int n_files, const 
     o.randomSeed = opt->random_seed;
     o.trainingMode = opt->training_mode != 0;
     o.loaderThreads = opt->loader_threads;
+    o.shardRank = opt->shard_rank;
+    o.shardCount = opt->shard_count < 1 ? 1 : opt->shard_count;
     b2_data *d = new b2_data;
     std::string err = d->ds.open(files, o);
     if (!err.empty()) {
@@ -125,21 +127,27 @@ int b2_net_train_epoch(b2_net *net, b2_data *data, float learning_rate, float mo
     int rc = b2_data_next_fraction(data, &cur);
     if (rc < 0) return rc;
     const bool train = learning_rate >= 0.0f;
-    if (rc == B2_OK && train) B2_TRY(b2_net_prefetch_fraction(net, cur.max_seq_length, cur.num_sequences, cur.seq_lengths, cur.inputs, cur.targets));
+    // a sharded data set may hand this rank an empty fraction (fewer sequences than shards at the end of
+    // an epoch): the rank then only takes part in the gradient sum
+    if (rc == B2_OK && train && cur.num_sequences > 0)
+        B2_TRY(b2_net_prefetch_fraction(net, cur.max_seq_length, cur.num_sequences, cur.seq_lengths, cur.inputs, cur.targets));
     while (rc == B2_OK) {
         double e = 0.0;
         int rcNext;
         if (train) {
             // enqueue this fraction's step, then start the next fraction's copy while it runs
-            B2_TRY(b2_net_train_step_prefetched(net, learning_rate, momentum, nullptr));
+            if (cur.num_sequences > 0) B2_TRY(b2_net_train_step_prefetched(net, learning_rate, momentum, nullptr));
+            else B2_TRY(b2_net_train_step_empty(net, learning_rate, momentum));
             rcNext = b2_data_next_fraction(data, &nxt);
             if (rcNext < 0) return rcNext;
-            if (rcNext == B2_OK)
+            if (rcNext == B2_OK && nxt.num_sequences > 0)
                 B2_TRY(b2_net_prefetch_fraction(net, nxt.max_seq_length, nxt.num_sequences, nxt.seq_lengths, nxt.inputs, nxt.targets));
-            B2_TRY(b2_net_read_error(net, &e));
+            if (cur.num_sequences > 0) B2_TRY(b2_net_read_error(net, &e));
         } else {
-            B2_TRY(b2_net_load_fraction(net, cur.max_seq_length, cur.num_sequences, cur.seq_lengths, cur.inputs, cur.targets));
-            B2_TRY(b2_net_forward(net, &e));
+            if (cur.num_sequences > 0) {
+                B2_TRY(b2_net_load_fraction(net, cur.max_seq_length, cur.num_sequences, cur.seq_lengths, cur.inputs, cur.targets));
+                B2_TRY(b2_net_forward(net, &e));
+            }
             rcNext = b2_data_next_fraction(data, &nxt);
             if (rcNext < 0) return rcNext;
         }
@@ -147,6 +155,13 @@ int b2_net_train_epoch(b2_net *net, b2_data *data, float learning_rate, float mo
         nFrames += cur.total_frames;
         cur = nxt;
         rc = rcNext;
+    }
+    // data-parallel: the epoch's error and frame count are those of all shards
+    if (b2_dp_world_size(net) > 1) {
+        double fr = (double)nFrames;
+        B2_TRY(b2_dp_allreduce_scalar(net, &errSum));
+        B2_TRY(b2_dp_allreduce_scalar(net, &fr));
+        nFrames = (long long)(fr + 0.5);
     }
     if (error) *error = errSum;
     if (frames) *frames = nFrames;

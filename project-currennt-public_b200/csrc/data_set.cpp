@@ -104,6 +104,7 @@ std::string DataSet::open(const std::vector<std::string> &ncfiles, const DataSet
     m_opt = opt;
     if (opt.fraction <= 0 || opt.fraction > 1) return "Invalid fraction";
     if (opt.parallelSequences < 1) return "Invalid number of parallel sequences";
+    if (opt.shardCount < 1 || opt.shardRank < 0 || opt.shardRank >= opt.shardCount) return "Invalid shard rank / count";
     if (ncfiles.empty()) return "No data files given";
     if (m_opt.loaderThreads <= 0) {
         unsigned hc = std::thread::hardware_concurrency();
@@ -232,7 +233,7 @@ void DataSet::_shuffleSequences() { random_shuffle_ref(m_sequences, m_opt.random
 void DataSet::_shuffleFractions() {
     std::vector<std::vector<sequence_t> > fractions;
     for (size_t i = 0; i < m_sequences.size(); ++i) {
-        if (i % m_opt.parallelSequences == 0) fractions.resize(fractions.size() + 1);
+        if (i % ((size_t)m_opt.parallelSequences * m_opt.shardCount) == 0) fractions.resize(fractions.size() + 1);
         fractions.back().push_back(m_sequences[i]);
     }
     random_shuffle_ref(fractions, m_opt.randomSeed);
@@ -257,15 +258,27 @@ void DataSet::_makeFractionTask(int firstSeqIdx, FractionView &frac) {
     frac.originalSeqIdx.clear();
     frac.seqTags.clear();
     frac.fracTotalLength = 0;
-    for (int seqIdx = firstSeqIdx; seqIdx < firstSeqIdx + P; ++seqIdx) {
-        if (seqIdx < (int)m_sequences.size()) {
-            frac.maxSeqLength = std::max(frac.maxSeqLength, m_sequences[seqIdx].length);
-            frac.minSeqLength = std::min(frac.minSeqLength, m_sequences[seqIdx].length);
-            frac.seqLengths.push_back(m_sequences[seqIdx].length);
-            frac.originalSeqIdx.push_back(m_sequences[seqIdx].originalSeqIdx);
-            frac.seqTags.push_back(m_sequences[seqIdx].seqTag);
-            frac.fracTotalLength += m_sequences[seqIdx].length;
-        }
+    // position k of the (global) fraction belongs to shard k % S in even rounds, S-1 - k % S in odd rounds
+    const int S = m_opt.shardCount;
+    std::vector<int> mine;
+    for (int k = 0; k < P * S; ++k) {
+        const int seqIdx = firstSeqIdx + k;
+        if (seqIdx >= (int)m_sequences.size()) break;
+        const int pos = k % S, owner = ((k / S) % 2 == 0) ? pos : S - 1 - pos;
+        if (owner == m_opt.shardRank) mine.push_back(seqIdx);
+    }
+    for (int seqIdx : mine) {
+        frac.maxSeqLength = std::max(frac.maxSeqLength, m_sequences[seqIdx].length);
+        frac.minSeqLength = std::min(frac.minSeqLength, m_sequences[seqIdx].length);
+        frac.seqLengths.push_back(m_sequences[seqIdx].length);
+        frac.originalSeqIdx.push_back(m_sequences[seqIdx].originalSeqIdx);
+        frac.seqTags.push_back(m_sequences[seqIdx].seqTag);
+        frac.fracTotalLength += m_sequences[seqIdx].length;
+    }
+    if (mine.empty()) {   // more shards than sequences in the last fraction: this shard sits the step out
+        frac.maxSeqLength = frac.minSeqLength = 0;
+        frac.numSequences = 0;
+        return;
     }
     frac.numSequences = (int)frac.seqLengths.size();
     const int T = frac.maxSeqLength, nSeq = frac.numSequences;
@@ -281,7 +294,7 @@ void DataSet::_makeFractionTask(int firstSeqIdx, FractionView &frac) {
                 float *din = frac.inputs + slot * inSize;
                 float *dout = frac.outputs + slot * outSize;
                 if (i < nSeq && t < frac.seqLengths[i]) {
-                    const sequence_t &seq = m_sequences[firstSeqIdx + i];
+                    const sequence_t &seq = m_sequences[mine[i]];
                     m_files[seq.file]->readFloatRows(*m_inVar[seq.file], (uint64_t)(seq.frameBegin + t), 1, din);
                     m_files[seq.file]->readFloatRows(*m_outVar[seq.file], (uint64_t)(seq.frameBegin + t), 1, dout);
                     const int len = frac.seqLengths[i];
@@ -339,7 +352,7 @@ const FractionView *DataSet::getNextFraction() {
     const FractionView *frac = nullptr;
     if (m_curFirstSeqIdx < (int)m_sequences.size()) {
         frac = &m_frac[m_readyBuf];
-        m_curFirstSeqIdx += m_opt.parallelSequences;
+        m_curFirstSeqIdx += m_opt.parallelSequences * m_opt.shardCount;
         if (m_curFirstSeqIdx < (int)m_sequences.size()) _startTask(false, m_curFirstSeqIdx);
         else _startTask(true, 0);
     } else {

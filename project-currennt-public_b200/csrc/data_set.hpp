@@ -31,6 +31,10 @@ struct DataSetOptions {
     unsigned randomSeed = 0;
     bool trainingMode = true;       // sort the segments by length
     int loaderThreads = 0;          // 0: min(8, hardware threads)
+    // data-parallel sharding: a fraction then spans parallelSequences * shardCount sequences, dealt to the
+    // shards in snake order (0 1 2 .. S-1, S-1 .. 1 0, ...) so that frames and longest lengths balance;
+    // this data set assembles shard shardRank's sequences only
+    int shardRank = 0, shardCount = 1;
 };
 
 // what DataSetFraction exposes to Layer::loadSequences

@@ -456,6 +456,22 @@ int NeuralNetwork::computeBackwardPass() {
     }
     return B2_OK;
 }
+int NeuralNetwork::trainStepEmpty(float lr, float mom) {
+    if (!dp) { set_error("b2_net_train_step_empty: no data-parallel communicator attached"); return B2_ERR_STATE; }
+    for (int i = (int)layers.size() - 1; i >= 1; --i) {
+        TrainableLayer *t = dynamic_cast<TrainableLayer *>(layers[i].get());
+        if (!t) continue;
+        B2_TRY(fill_zero(t->weightUpdates(), t->numWeights() * sizeof(float), stream));
+        B2_CUDA(cudaEventRecord(gradReady[i], stream));
+        B2_CUDA(cudaStreamWaitEvent(commStream, gradReady[i], 0));
+        B2_TRY(dp_allreduce_sum(*this, t->weightUpdates(), t->numWeights(), commStream));
+    }
+    B2_CUDA(cudaEventRecord(gradReady[0], commStream));
+    B2_CUDA(cudaStreamWaitEvent(stream, gradReady[0], 0));
+    frac.realFrames = 0;
+    return updateWeights(lr, mom);
+}
+
 // Optimizer constructor, option part (optimizers/Optimizer.cu:421-457): AdaGrad statistics start at
 // OP_ADAGRADFACTOR, Adam's first and second moments at zero
 int NeuralNetwork::setOptimizerOption(int option) {
@@ -649,6 +665,8 @@ int b2_net_forward(b2_net *n, double *error) {
 }
 int b2_net_backward(b2_net *n) { return n ? n->net.computeBackwardPass() : B2_ERR_BAD_ARG; }
 int b2_net_update_weights(b2_net *n, float lr, float mom) { return n ? n->net.updateWeights(lr, mom) : B2_ERR_BAD_ARG; }
+int b2_net_train_step_empty(b2_net *n, float lr, float mom) { return n ? n->net.trainStepEmpty(lr, mom) : B2_ERR_BAD_ARG; }
+int b2_dp_world_size(const b2_net *n) { return n ? dp_world(n->net) : 1; }
 int b2_net_set_optimizer(b2_net *n, int option) { return n ? n->net.setOptimizerOption(option) : B2_ERR_BAD_ARG; }
 int b2_net_get_optimizer_stats(b2_net *n, int i, float *host, size_t capacity, size_t *count) {
     TrainableLayer *t = trainable(n, i);

@@ -148,6 +148,8 @@ public:
     int calculateError(double *hostError);
     int computeBackwardPass();
     int updateWeights(float lr, float mom);
+    // data-parallel step of a rank that has no sequence in the current fraction: zero gradients into the sums, update
+    int trainStepEmpty(float lr, float mom);
     // optimizer option of the reference (MacroDefine.hpp:32-37): 0 plain, 1 AdaGrad, 2 average gradient,
     // 3 SGD accumulating AdaGrad statistics, 5 Adam
     int setOptimizerOption(int option);

@@ -272,3 +272,35 @@ def test_workload_written_as_nc_reads_back_as_the_same_fraction(tmp_path):
     assert np.array_equal(f["inputs"].reshape(-1), np.asarray(wl["x"]).reshape(-1)[:f["inputs"].size])
     assert np.array_equal(f["targets"].reshape(-1), np.asarray(wl["tg"]).reshape(-1)[:f["targets"].size])
     assert ds.next_fraction() is None
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_shards_deal_every_fraction_in_snake_order(tmp_path, world):
+    """Data-parallel sharding: with S shards a fraction spans P*S sequences; position k goes to shard
+    k % S in even rounds and S-1 - k % S in odd rounds (the rule of b2lstm.dp.shard_indices); every shard
+    pads to its own longest sequence; shards without a sequence get an empty fraction."""
+    from b2lstm.dp import shard_indices
+    lens = [5, 3, 9, 4, 7, 2, 6, 11, 1, 8, 10, 13, 12]
+    tags, lens, x, y = make_corpus(21, lens)
+    path = str(tmp_path / "d.nc")
+    b2lstm.write_nc(path, tags, lens, x, y)
+    P = 2
+    starts = np.concatenate([[0], np.cumsum(lens)[:-1]])
+    source = {(t, 0): (x, y, int(s)) for t, s in zip(tags, starts)}
+    order = [tags[i] for i in sorted(range(len(lens)), key=lambda i: lens[i])]
+    sets = [b2lstm.DataSet(path, P, shard_rank=r, shard_count=world) for r in range(world)]
+    n_frac = -(-len(lens) // (P * world))
+    total = 0
+    for k in range(n_frac):
+        glob = order[k * P * world:(k + 1) * P * world]
+        for r in range(world):
+            f = sets[r].next_fraction()            # the views stay valid for two more fractions only: check now
+            want = [glob[i] for i in shard_indices(len(glob), r, world)]
+            assert f["tags"] == want
+            if want:
+                check_fraction(f, P, source)
+            else:
+                assert f["num_sequences"] == 0 and f["T"] == 0
+            total += f["total_frames"]
+    assert all(ds.next_fraction() is None for ds in sets)
+    assert total == sum(lens)
