@@ -174,7 +174,10 @@ def test_optimizer_options_follow_the_reference_formulas(option):
             w[i] = (w[i] + delta[i]).astype(f32)
             got = net.get_weights(i)
             assert np.allclose(got, w[i], rtol=2e-5, atol=1e-7), (option, k, i, np.abs(got - w[i]).max())
-            assert np.allclose(net.optimizer_stats(i), stats[i], rtol=2e-5, atol=1e-12)
+            if option != 2:
+                assert np.allclose(net.optimizer_stats(i), stats[i], rtol=2e-5, atol=1e-6 * np.abs(stats[i]).max())
+            else:
+                assert net.optimizer_stats(i).size == 0
             w[i] = got                       # follow the device weights: the next gradients come from them
             net.set_weight_deltas(i, delta[i])
     net.set_optimizer(0)
