@@ -180,6 +180,12 @@ int b2_net_set_optimizer(b2_net *net, int option);
 /* Optimizer::m_weightStats of one layer (AdaGrad: one float per weight; Adam: m and v interleaved),
  * the "optimizer_status_vector" of an autosave.  host_out may be NULL to ask for *count only. */
 int b2_net_get_optimizer_stats(b2_net *net, int layer, float *host_out, size_t capacity, size_t *count);
+/* Batch (non-stochastic) learning, i.e. the reference without --hybrid_online_batch
+ * (optimizers/Optimizer.cu:186-196, 243-245): after every backward pass the optimizer's copy of the
+ * weight updates takes (first != 0) or adds the layer gradients; after the last fraction ONE update
+ * runs on the sum, with a frame count of 1 for the shaping options. */
+int b2_net_accumulate_weight_updates(b2_net *net, int first);
+int b2_net_update_weights_batch(b2_net *net, float learning_rate, float momentum);
 /* One iteration of the minibatch loop of Optimizer::_processDataSet (Optimizer.cu:68-231) with
  * hybrid_online_batch: load, forward, error, backward, [all-reduce], update.  *error may be NULL. */
 int b2_net_train_step(b2_net *net, int T, int n_seqs, const int *seq_lens, const float *host_inputs,
@@ -243,6 +249,8 @@ int b2_dp_world_size(const b2_net *net);
 /* The train step of a rank that has NO sequence in the current fraction (a sharded data set near the
  * end of an epoch): zero gradients go into the all-reduce, the update runs as on the other ranks. */
 int b2_net_train_step_empty(b2_net *net, float learning_rate, float momentum);
+/* Its backward part alone: zero gradients into the all-reduce of every layer (batch learning). */
+int b2_net_backward_empty(b2_net *net);
 
 /* ------------------------------------------------------------------------------------------
  * Data sets: the toolkit's .nc files (netCDF classic; CURRENNT_codes/README section 5) read
@@ -307,6 +315,10 @@ void b2_data_reseed(unsigned seed);
  * forward and error only). */
 int b2_net_train_epoch(b2_net *net, b2_data *data, float learning_rate, float momentum, double *error,
                        long long *frames);
+/* The same pass as batch learning (no --hybrid_online_batch): gradients of all fractions are summed,
+ * the weights change once, after the last fraction. */
+int b2_net_train_epoch_batch(b2_net *net, b2_data *data, float learning_rate, float momentum, double *error,
+                             long long *frames);
 
 /* ------------------------------------------------------------------------------------------
  * Network export, and the training run around the epoch loop: validation-based early
@@ -335,6 +347,7 @@ typedef struct {
     int max_epochs_no_best;    /* --max_epochs_no_best */
     int validate_every;        /* --validate_every */
     int test_every;            /* --test_every */
+    int batch_learning;        /* non-zero: the reference WITHOUT --hybrid_online_batch (one update per epoch) */
 } b2_optimizer_options;
 typedef struct {
     int finished, cur_epoch, epochs_since_lowest_error;

@@ -4,8 +4,8 @@ generates the synthetic workloads and launches processes.  There is no CPU fallb
 works without a GPU (symbols can be inspected), every compute call needs one.
 """
 from .lib import (B2Error, LstmLayer, Net, lib, library_path, lstm_num_weights, matrix_multiply, matrix_multiply_noalloc,
-                  dp_unique_id, DataSet, data_reseed, train_epoch, write_nc, Optimizer)
+                  dp_unique_id, DataSet, data_reseed, train_epoch, train_epoch_batch, write_nc, Optimizer)
 from . import workloads
 
 __all__ = ["B2Error", "LstmLayer", "Net", "lib", "library_path", "lstm_num_weights", "matrix_multiply", "matrix_multiply_noalloc",
-           "dp_unique_id", "DataSet", "data_reseed", "train_epoch", "write_nc", "Optimizer", "workloads"]
+           "dp_unique_id", "DataSet", "data_reseed", "train_epoch", "train_epoch_batch", "write_nc", "Optimizer", "workloads"]

@@ -61,6 +61,10 @@ SIGNATURES = {
     "b2_net_update_weights": (C.c_int, [C.c_void_p, C.c_float, C.c_float]),
     "b2_net_set_optimizer": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_net_get_optimizer_stats": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "b2_net_accumulate_weight_updates": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2_net_update_weights_batch": (C.c_int, [C.c_void_p, C.c_float, C.c_float]),
+    "b2_net_train_epoch_batch": (C.c_int, [C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.POINTER(C.c_double),
+                                           C.POINTER(C.c_longlong)]),
     "b2_net_train_step": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float,
                                     C.c_float, C.POINTER(C.c_double)]),
     "b2_net_prefetch_fraction": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -84,6 +88,7 @@ SIGNATURES = {
     "b2_dp_allreduce_scalar": (C.c_int, [C.c_void_p, C.POINTER(C.c_double)]),
     "b2_dp_world_size": (C.c_int, [C.c_void_p]),
     "b2_net_train_step_empty": (C.c_int, [C.c_void_p, C.c_float, C.c_float]),
+    "b2_net_backward_empty": (C.c_int, [C.c_void_p]),
     "b2_data_open": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_char_p), C.c_int, C.c_void_p]),
     "b2_data_close": (None, [C.c_void_p]),
     "b2_data_info": (C.c_int, [C.c_void_p, _ip, C.POINTER(C.c_longlong), _ip, _ip, _ip, _ip]),
@@ -281,6 +286,12 @@ class Net:
 
     def backward(self):
         _check(lib().b2_net_backward(self.h))
+
+    def accumulate_weight_updates(self, first):
+        _check(lib().b2_net_accumulate_weight_updates(self.h, int(first)))
+
+    def update_weights_batch(self, lr, momentum):
+        _check(lib().b2_net_update_weights_batch(self.h, lr, momentum))
 
     def update_weights(self, lr, momentum):
         _check(lib().b2_net_update_weights(self.h, lr, momentum))
@@ -498,6 +509,13 @@ def train_epoch(net, data, lr, momentum):
     return e.value, n.value
 
 
+def train_epoch_batch(net, data, lr, momentum):
+    """b2_net_train_epoch_batch (batch learning: one update per epoch): (error, frames)"""
+    e, n = C.c_double(), C.c_longlong()
+    _check(lib().b2_net_train_epoch_batch(net.h, data.h, lr, momentum, C.byref(e), C.byref(n)))
+    return e.value, n.value
+
+
 def write_nc(path, seq_tags, seq_lengths, inputs, targets, output_means=None, output_stdevs=None, version=2):
     """Writes a data set in the toolkit's .nc layout (netCDF classic via scipy, as the reference's
     pyTools/dataTools/ncDataHandle.py does): inputs [numTimesteps, inputPattSize], targets
@@ -533,7 +551,8 @@ def write_nc(path, seq_tags, seq_lengths, inputs, targets, output_means=None, ou
 
 class _OptimizerOptions(C.Structure):
     _fields_ = [("learning_rate", C.c_float), ("momentum", C.c_float), ("max_epochs", C.c_int),
-                ("max_epochs_no_best", C.c_int), ("validate_every", C.c_int), ("test_every", C.c_int)]
+                ("max_epochs_no_best", C.c_int), ("validate_every", C.c_int), ("test_every", C.c_int),
+                ("batch_learning", C.c_int)]
 
 
 class _OptimizerState(C.Structure):
@@ -549,8 +568,9 @@ class Optimizer:
     train() runs one epoch (plus validation / test passes when due) and returns True when finished."""
 
     def __init__(self, net, training_set, validation_set=None, test_set=None, learning_rate=1e-5, momentum=0.9,
-                 max_epochs=-1, max_epochs_no_best=20, validate_every=1, test_every=1):
-        opt = _OptimizerOptions(learning_rate, momentum, max_epochs, max_epochs_no_best, validate_every, test_every)
+                 max_epochs=-1, max_epochs_no_best=20, validate_every=1, test_every=1, batch_learning=False):
+        opt = _OptimizerOptions(learning_rate, momentum, max_epochs, max_epochs_no_best, validate_every, test_every,
+                                int(batch_learning))
         self.h = C.c_void_p()
         self._keep = (net, training_set, validation_set, test_set)
         _check(lib().b2_optimizer_create(C.byref(self.h), net.h, training_set.h,

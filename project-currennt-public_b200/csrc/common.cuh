@@ -118,6 +118,8 @@ int sgd_update(float *w, float *g, float *delta, size_t n, float lr, float mom, 
 int sgd_update_opt(float *w, float *g, float *delta, float *stats, size_t n, float lr, float mom, int option,
                    const float *frac_len_dev, float beta1_accum, float beta2_accum, cudaStream_t st);
 int fill_value(float *p, size_t n, float v, cudaStream_t st);
+// acc = g (first) or acc + g
+int accumulate(float *acc, const float *g, size_t n, bool first, cudaStream_t st);
 int fill_zero(void *p, size_t bytes, cudaStream_t st);
 
 // ---- LSTM recurrence (lstm_step.cu, lstm_persistent.cu) -------------------------------------------

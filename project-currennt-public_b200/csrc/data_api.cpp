@@ -168,4 +168,44 @@ int b2_net_train_epoch(b2_net *net, b2_data *data, float learning_rate, float mo
     return B2_OK;
 }
 
+// Optimizer::_processDataSet without hybrid_online_batch: forward, error, backward and accumulation per
+// fraction, one update at the end
+int b2_net_train_epoch_batch(b2_net *net, b2_data *data, float learning_rate, float momentum, double *error, long long *frames) {
+    if (!net || !data) { b2::set_error("b2_net_train_epoch_batch: null handle"); return B2_ERR_BAD_ARG; }
+    const double nSeqTotal = (double)data->ds.totalSequences();
+    double errSum = 0.0;
+    long long nFrames = 0;
+    bool first = true;
+    b2_fraction cur;
+    int rc;
+    while ((rc = b2_data_next_fraction(data, &cur)) == B2_OK) {
+        double e = 0.0;
+        if (cur.num_sequences == 0) {
+            // an empty shard: this rank still takes part in the gradient sums of the fraction
+            if (b2_dp_world_size(net) <= 1) continue;
+            B2_TRY(b2_net_backward_empty(net));
+        } else {
+            B2_TRY(b2_net_load_fraction(net, cur.max_seq_length, cur.num_sequences, cur.seq_lengths, cur.inputs, cur.targets));
+            B2_TRY(b2_net_forward(net, &e));
+            B2_TRY(b2_net_backward(net));
+        }
+        B2_TRY(b2_net_accumulate_weight_updates(net, first ? 1 : 0));
+        B2_TRY(b2_net_synchronize(net));        // the fraction's host buffers are recycled by the data set
+        first = false;
+        if (e == e) errSum += e / nSeqTotal;
+        nFrames += cur.total_frames;
+    }
+    if (rc < 0) return rc;
+    if (!first) B2_TRY(b2_net_update_weights_batch(net, learning_rate, momentum));
+    if (b2_dp_world_size(net) > 1) {
+        double fr = (double)nFrames;
+        B2_TRY(b2_dp_allreduce_scalar(net, &errSum));
+        B2_TRY(b2_dp_allreduce_scalar(net, &fr));
+        nFrames = (long long)(fr + 0.5);
+    }
+    if (error) *error = errSum;
+    if (frames) *frames = nFrames;
+    return B2_OK;
+}
+
 }  // extern "C"

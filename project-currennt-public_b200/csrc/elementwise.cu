@@ -161,6 +161,11 @@ __global__ void sgd_update_opt_kernel(float *__restrict__ w, float *__restrict__
         w[i] = w[i] + dl;
     }
 }
+// m_curWeightUpdates of batch learning (optimizers/Optimizer.cu:186-196): copy on the first fraction, add after
+__global__ void accumulate_kernel(float *__restrict__ acc, const float *__restrict__ g, size_t n, int first) {
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) acc[i] = first ? g[i] : acc[i] + g[i];
+}
 __global__ void fill_value_kernel(float *p, size_t n, float v) {
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = v;
@@ -251,6 +256,14 @@ int sgd_update_opt(float *w, float *g, float *delta, float *stats, size_t n, flo
     if (!n) return B2_OK;
     sgd_update_opt_kernel<<<grid_for(n, 256), 256, 0, st>>>(w, g, delta, stats, n, lr, mom, option, frac_len_dev, beta1_accum,
                                                          beta2_accum);
+    count_launch();
+    B2_CUDA(cudaGetLastError());
+    return B2_OK;
+}
+
+int accumulate(float *acc, const float *g, size_t n, bool first, cudaStream_t st) {
+    if (!n) return B2_OK;
+    accumulate_kernel<<<grid_for(n, 256), 256, 0, st>>>(acc, g, n, first ? 1 : 0);
     count_launch();
     B2_CUDA(cudaGetLastError());
     return B2_OK;

@@ -68,6 +68,7 @@ TrainableLayer::~TrainableLayer() {
     cudaFree(weightUpdates_);
     cudaFree(weightDeltas_);
     cudaFree(weightStats_);
+    cudaFree(weightAccum_);
 }
 int TrainableLayer::allocateWeights(size_t n) {
     nW_ = n;
@@ -77,6 +78,13 @@ int TrainableLayer::allocateWeights(size_t n) {
     B2_CUDA(cudaMemset(weights_, 0, n * sizeof(float)));
     B2_CUDA(cudaMemset(weightUpdates_, 0, n * sizeof(float)));
     B2_CUDA(cudaMemset(weightDeltas_, 0, n * sizeof(float)));
+    return B2_OK;
+}
+
+int TrainableLayer::allocateAccum() {
+    if (weightAccum_) return B2_OK;
+    B2_CUDA(cudaMalloc(&weightAccum_, nW_ * sizeof(float)));
+    B2_CUDA(cudaMemset(weightAccum_, 0, nW_ * sizeof(float)));
     return B2_OK;
 }
 
@@ -456,8 +464,40 @@ int NeuralNetwork::computeBackwardPass() {
     }
     return B2_OK;
 }
-int NeuralNetwork::trainStepEmpty(float lr, float mom) {
-    if (!dp) { set_error("b2_net_train_step_empty: no data-parallel communicator attached"); return B2_ERR_STATE; }
+// Optimizer::_processDataSet without hybrid_online_batch (optimizers/Optimizer.cu:186-196, 243-245): the
+// optimizer's copy of the weight updates sums the fractions' gradients; ONE update, with frame count 1,
+// follows the last fraction
+int NeuralNetwork::accumulateWeightUpdates(bool first) {
+    for (size_t i = 1; i < layers.size(); ++i) {
+        TrainableLayer *t = dynamic_cast<TrainableLayer *>(layers[i].get());
+        if (!t) continue;
+        B2_TRY(t->allocateAccum());
+        B2_TRY(accumulate(t->weightAccum(), t->weightUpdates(), t->numWeights(), first, stream));
+    }
+    return B2_OK;
+}
+int NeuralNetwork::updateWeightsBatch(float lr, float mom) {
+    for (size_t i = 1; i < layers.size(); ++i) {
+        TrainableLayer *t = dynamic_cast<TrainableLayer *>(layers[i].get());
+        if (!t) continue;
+        if (!t->weightAccum()) { set_error("b2_net_update_weights_batch: nothing accumulated"); return B2_ERR_STATE; }
+        B2_CUDA(cudaMemcpyAsync(t->weightUpdates(), t->weightAccum(), t->numWeights() * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+    }
+    // _updateWeights(1): the shaping options see a frame count of one; the gradients are already summed
+    // over the ranks, so the count is not
+    DpComm *keep = dp;
+    const long frames = frac.realFrames;
+    frac.realFrames = 1;
+    dp = nullptr;
+    const int rc = updateWeights(lr, mom);
+    dp = keep;
+    frac.realFrames = frames;
+    return rc;
+}
+
+// a rank without a sequence in the current fraction: zero gradients into the all-reduce of every layer
+int NeuralNetwork::computeBackwardPassEmpty() {
+    if (!dp) { set_error("b2_net_backward_empty: no data-parallel communicator attached"); return B2_ERR_STATE; }
     for (int i = (int)layers.size() - 1; i >= 1; --i) {
         TrainableLayer *t = dynamic_cast<TrainableLayer *>(layers[i].get());
         if (!t) continue;
@@ -469,6 +509,10 @@ int NeuralNetwork::trainStepEmpty(float lr, float mom) {
     B2_CUDA(cudaEventRecord(gradReady[0], commStream));
     B2_CUDA(cudaStreamWaitEvent(stream, gradReady[0], 0));
     frac.realFrames = 0;
+    return B2_OK;
+}
+int NeuralNetwork::trainStepEmpty(float lr, float mom) {
+    B2_TRY(computeBackwardPassEmpty());
     return updateWeights(lr, mom);
 }
 
@@ -665,6 +709,9 @@ int b2_net_forward(b2_net *n, double *error) {
 }
 int b2_net_backward(b2_net *n) { return n ? n->net.computeBackwardPass() : B2_ERR_BAD_ARG; }
 int b2_net_update_weights(b2_net *n, float lr, float mom) { return n ? n->net.updateWeights(lr, mom) : B2_ERR_BAD_ARG; }
+int b2_net_accumulate_weight_updates(b2_net *n, int first) { return n ? n->net.accumulateWeightUpdates(first != 0) : B2_ERR_BAD_ARG; }
+int b2_net_update_weights_batch(b2_net *n, float lr, float mom) { return n ? n->net.updateWeightsBatch(lr, mom) : B2_ERR_BAD_ARG; }
+int b2_net_backward_empty(b2_net *n) { return n ? n->net.computeBackwardPassEmpty() : B2_ERR_BAD_ARG; }
 int b2_net_train_step_empty(b2_net *n, float lr, float mom) { return n ? n->net.trainStepEmpty(lr, mom) : B2_ERR_BAD_ARG; }
 int b2_dp_world_size(const b2_net *n) { return n ? dp_world(n->net) : 1; }
 int b2_net_set_optimizer(b2_net *n, int option) { return n ? n->net.setOptimizerOption(option) : B2_ERR_BAD_ARG; }

@@ -67,6 +67,8 @@ public:
     float *weightUpdates() { return weightUpdates_; }
     float *weightDeltas() { return weightDeltas_; }
     float *weightStats() { return weightStats_; }
+    float *weightAccum() { return weightAccum_; }
+    int allocateAccum();
     size_t statsFloats() const { return statsFloats_; }
     // AdaGrad / Adam statistics (Optimizer::m_weightStats): n floats filled with `init`, or 2n zeros for Adam
     int allocateStats(size_t floats, float init, cudaStream_t st);
@@ -77,7 +79,7 @@ public:
 protected:
     size_t nW_ = 0;
     float bias_, learningRate_;
-    float *weights_ = nullptr, *weightUpdates_ = nullptr, *weightDeltas_ = nullptr, *weightStats_ = nullptr;
+    float *weights_ = nullptr, *weightUpdates_ = nullptr, *weightDeltas_ = nullptr, *weightStats_ = nullptr, *weightAccum_ = nullptr;
     size_t statsFloats_ = 0;
 };
 
@@ -149,7 +151,11 @@ public:
     int computeBackwardPass();
     int updateWeights(float lr, float mom);
     // data-parallel step of a rank that has no sequence in the current fraction: zero gradients into the sums, update
+    int computeBackwardPassEmpty();
     int trainStepEmpty(float lr, float mom);
+    // batch (non-stochastic) learning: gradients of the fractions of an epoch are accumulated, one update at its end
+    int accumulateWeightUpdates(bool first);
+    int updateWeightsBatch(float lr, float mom);
     // optimizer option of the reference (MacroDefine.hpp:32-37): 0 plain, 1 AdaGrad, 2 average gradient,
     // 3 SGD accumulating AdaGrad statistics, 5 Adam
     int setOptimizerOption(int option);

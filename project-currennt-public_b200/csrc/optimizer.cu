@@ -292,7 +292,8 @@ int b2_optimizer_train(b2_optimizer *o, int *finished) {
         long long frames = 0;
         int nSeq = 0;
         long long nSteps = 0;
-        B2_TRY(b2_net_train_epoch(o->net, o->trainingSet, o->opt.learning_rate, o->opt.momentum, &err, &frames));
+        if (o->opt.batch_learning) B2_TRY(b2_net_train_epoch_batch(o->net, o->trainingSet, o->opt.learning_rate, o->opt.momentum, &err, &frames));
+        else B2_TRY(b2_net_train_epoch(o->net, o->trainingSet, o->opt.learning_rate, o->opt.momentum, &err, &frames));
         o->curTrainingError = (float)err;
         B2_TRY(b2_data_info(o->trainingSet, &nSeq, &nSteps, nullptr, nullptr, nullptr, nullptr));
         o->curTrainingErrorPerFrame = o->curTrainingError * ((float)nSeq / (float)nSteps);

@@ -183,3 +183,35 @@ def test_optimizer_options_follow_the_reference_formulas(option):
     net.set_optimizer(0)
     assert net.optimizer_stats(1).size == 0
     net.close()
+
+
+def test_batch_learning_sums_the_epoch_and_updates_once(tmp_path):
+    """The reference without --hybrid_online_batch: the gradients of all fractions of an epoch are summed
+    and ONE update follows.  Checked against the sum of the per-fraction gradients taken separately."""
+    import b2lstm
+    from b2lstm import workloads
+    w_true = np.random.default_rng(0).standard_normal((7, 3)).astype(np.float32)
+    path = corpus(tmp_path, "batch.nc", [20, 35, 28, 31, 25, 22, 38], 4, w_true)
+    P = 3
+    w = workloads.make_weights(LAYERS, 9, 0.1)
+    lr, mom = 1e-4, 0.9
+
+    net = b2lstm.Net(LAYERS, P, 40)
+    for i, wi in w.items():
+        net.set_weights(i, wi)
+    ds = b2lstm.DataSet(path, P)
+    gsum = {i: np.zeros_like(wi) for i, wi in w.items()}
+    err = 0.0
+    for f in ds.epoch():
+        net.load_fraction(f["seq_lengths"], np.array(f["inputs"]), np.array(f["targets"]))
+        err += net.forward() / ds.total_sequences
+        net.backward()
+        for i in w:
+            gsum[i] = gsum[i] + net.weight_updates(i)
+    got_err, frames = b2lstm.train_epoch_batch(net, ds, lr, mom)
+    assert frames == ds.total_timesteps and abs(got_err - err) <= 1e-6 * abs(err)      # weights were still the initial ones
+    for i, wi in w.items():
+        want = wi + (-np.float32(lr) * gsum[i]).astype(np.float32)
+        assert np.allclose(net.get_weights(i), want, rtol=1e-5, atol=1e-7)
+        assert np.allclose(net.weight_deltas(i), -np.float32(lr) * gsum[i], rtol=1e-4, atol=1e-9)
+    net.close()
