@@ -121,8 +121,42 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ void st_remote(uint32_t raddr, float v) {
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(raddr), "f"(v) : "memory");
+
+// shared-memory barrier with transaction count: the peers of a cluster deliver h with st.async, which both
+// writes the data into this block's shared memory and counts the bytes on this barrier
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded: false when the budget (about a second) ran out or another block reported a timeout
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, const int *status) {
+    for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 1023u) == 1023u && ld_status(status) != 0) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void st_async_v4(uint32_t raddr, float4 v, uint32_t rbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(raddr),
+                 "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(rbar)
+                 : "memory");
+}
+__device__ __forceinline__ void st_async_f32(uint32_t raddr, float v, uint32_t rbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" ::"r"(raddr), "f"(v), "r"(rbar)
+                 : "memory");
 }
 
 struct PersistArgs {
@@ -190,7 +224,18 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
     const int P = a.sh.P, T = a.sh.T, ls = a.sh.ls, D = a.sh.D;
     const LstmOffsets off = lstm_offsets(a.sh.pls, ls, ELS);
     u64 *xslot = a.xchg + (size_t)slot * 4 * ELS * PS;
-    // a peer's shared memory may only be touched once that peer has started running
+    // cluster transport: one transaction barrier per h buffer, a staging row to send 4 sequences of a unit at once
+    __shared__ __align__(8) unsigned long long hbar[2];
+    __shared__ float hstage[CL ? CELLS : 1];
+    unsigned hphase[2] = {0u, 0u};   // phases of each buffer's barrier this block has waited for
+    if constexpr (CL) {
+        if (tid == 0) {
+            mbar_init(smem_addr(&hbar[0]), 1);
+            mbar_init(smem_addr(&hbar[1]), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    }
+    // a peer's shared memory (and barriers) may only be touched once that peer has started running
     if constexpr (CL) { cluster_arrive(); cluster_wait(); }
 
     float wreg[4][KPT];
@@ -247,12 +292,24 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
                     }
                 }
             }
+            if constexpr (CL) {
+                // this step's h of all G blocks will arrive in buffer s&1 (the last step publishes nothing)
+                if (tid == 0 && s + 1 < T) mbar_expect_tx(smem_addr(&hbar[s & 1]), (uint32_t)(ELS * PS * sizeof(float)));
+            }
             // 2. h[t-1] of the whole group, 3. recurrent projection with register-resident weights
             if (!first) {
                 const float *hs = hs_all;
                 if constexpr (CL) {
-                    cluster_wait();   // every block of the cluster has stored its h[t-1] (release/acquire)
-                    hs = hs_all + ((s - 1) & 1) * ELS * PS;
+                    // every block of the cluster has delivered its h[t-1] into this block's buffer
+                    const int b = (s - 1) & 1;
+                    if (!mbar_wait_bounded(smem_addr(&hbar[b]), hphase[b] & 1u, a.status)) {
+                        gave_up = 1;
+                        atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT);
+                    }
+                    ++hphase[b];
+                    hs = hs_all + b * ELS * PS;
+                    const int dead_now = __syncthreads_or(gave_up);
+                    if (dead_now) { dead = true; break; }
                 } else {
                     const u64 *xb = xitem + (size_t)((s - 1) & 1) * ELS * PS;
                     float hv[(ELS * PS + NT - 1) / NT];
@@ -347,9 +404,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
                     cprev[ci] = cs;
                 }
                 if constexpr (CL) {
-                    const uint32_t la = smem_addr(hs_all + (s & 1) * ELS * PS + (j0 + jj) * PS + p);
-#pragma unroll
-                    for (int rk = 0; rk < G; ++rk) st_remote(map_to_rank(la, (uint32_t)rk), h);
+                    hstage[jj * PS + p] = h;
                 } else {
                     st_pair(xo + (size_t)p * ELS + j0 + jj, h, tag0 + (unsigned)s + 1u);
                 }
@@ -363,11 +418,29 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
                     a.y[f * ls + u] = h;
                 }
             }
-            if constexpr (CL) cluster_arrive();
+            if constexpr (CL) {
+                // thread (unit u, peer r) sends the PS sequences of unit u to block r of the cluster
+                __syncthreads();
+                if (s + 1 < T) {
+                    for (int idx = tid; idx < JB * G; idx += NT) {
+                        const int u = idx % JB, r = idx / JB;
+                        const uint32_t rbar = map_to_rank(smem_addr(&hbar[s & 1]), (uint32_t)r);
+                        const uint32_t la = smem_addr(hs_all + (s & 1) * ELS * PS + (j0 + u) * PS);
+                        if constexpr (PS % 4 == 0) {
+#pragma unroll
+                            for (int p4 = 0; p4 < PS / 4; ++p4)
+                                st_async_v4(map_to_rank(la + 16u * p4, (uint32_t)r),
+                                            *reinterpret_cast<const float4 *>(hstage + u * PS + 4 * p4), rbar);
+                        } else {
+#pragma unroll
+                            for (int p = 0; p < PS; ++p) st_async_f32(map_to_rank(la + 4u * p, (uint32_t)r), hstage[u * PS + p], rbar);
+                        }
+                    }
+                }
+            }
         }
-        // the last arrive of the item is matched here; it also keeps a fast block from overwriting
-        // buffers (or leaving the kernel) while a peer still reads them
-        if constexpr (CL) { if (T > 0) cluster_wait(); }
+        // nobody may overwrite a buffer (or leave the kernel) while a peer still reads or writes it
+        if constexpr (CL) { cluster_arrive(); cluster_wait(); }
         if (dead) break;
     }
 }
@@ -397,7 +470,17 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
     constexpr size_t XBUF = (size_t)G * G * CELLS;
     u64 *xslot = a.xchg + (size_t)slot * 4 * XBUF;
     const int kq = tid % KQ, rs = tid / KQ;
-    // a peer's shared memory may only be touched once that peer has started running
+    // cluster transport: one transaction barrier per receive buffer (see the forward kernel)
+    __shared__ __align__(8) unsigned long long ebar[2];
+    unsigned ephase[2] = {0u, 0u};
+    if constexpr (CL) {
+        if (tid == 0) {
+            mbar_init(smem_addr(&ebar[0]), 1);
+            mbar_init(smem_addr(&ebar[1]), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    }
+    // a peer's shared memory (and barriers) may only be touched once that peer has started running
     if constexpr (CL) { cluster_arrive(); cluster_wait(); }
 
     float wreg[4][RPT];
@@ -459,12 +542,24 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
                     }
                 }
             }
+            if constexpr (CL) {
+                // this step's partial sums of all G blocks will arrive in buffer s&1 (the last step sends nothing)
+                if (tid == 0 && !lastCall) mbar_expect_tx(smem_addr(&ebar[s & 1]), (uint32_t)(G * CELLS * sizeof(float)));
+            }
             // 2. partial sums of the recurrent error from every block of the group
             const float *pe = pe_all;
             if (!firstCall) {
                 if constexpr (CL) {
-                    cluster_wait();   // every block of the cluster has stored its partial sums (release/acquire)
-                    pe = pe_all + ((s - 1) & 1) * G * CELLS;
+                    // every block of the cluster has delivered its partial sums into this block's buffer
+                    const int b = (s - 1) & 1;
+                    if (!mbar_wait_bounded(smem_addr(&ebar[b]), ephase[b] & 1u, a.status)) {
+                        gave_up = 1;
+                        atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT);
+                    }
+                    ++ephase[b];
+                    pe = pe_all + b * G * CELLS;
+                    const int dead_now = __syncthreads_or(gave_up);
+                    if (dead_now) { dead = true; break; }
                 } else {
                     const u64 *xb = xitem + (size_t)((s - 1) & 1) * XBUF + (size_t)g * G * CELLS;
                     float pv[(G * CELLS + NT - 1) / NT];
@@ -549,7 +644,8 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
             auto send = [&](int k, int p, float v) {
                 const int cell = p * JB + (k % JB);
                 if constexpr (CL)
-                    st_remote(map_to_rank(smem_addr(pe_all + ((s & 1) * G + g) * CELLS + cell), (uint32_t)(k / JB)), v);
+                    st_async_f32(map_to_rank(smem_addr(pe_all + ((s & 1) * G + g) * CELLS + cell), (uint32_t)(k / JB)), v,
+                                 map_to_rank(smem_addr(&ebar[s & 1]), (uint32_t)(k / JB)));
                 else
                     st_pair(xo + ((size_t)(k / JB) * G + g) * CELLS + cell, v, tag);
             };
@@ -598,7 +694,6 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
                 send(k, p, v);
             }
             store_deltas();
-            if constexpr (CL) cluster_arrive();
         }
         // item boundary: nobody may overwrite a buffer (or leave the kernel) while a peer still reads it
         if constexpr (CL) { cluster_arrive(); cluster_wait(); }
