@@ -106,12 +106,17 @@ int b2_lstm_forward(b2_lstm *layer, const float *weights_dev, const float *x_dev
  * nobody reads); dw_dev: weightUpdates(), OVERWRITTEN, same layout as the weights. */
 int b2_lstm_backward(b2_lstm *layer, const float *weights_dev, const float *x_dev, const float *y_dev,
                      const float *dy_dev, float *dx_dev, float *dw_dev, b2_stream stream);
-/* Which recurrence kernels run: 0 = one launch per timestep; 1 = persistent kernel exchanging
- * through L2 (default; measured fastest on B200); 2 = persistent kernel exchanging through
- * distributed shared memory where a group fits a thread-block cluster (128 or 256 units per
- * direction), through L2 otherwise; 3 = tensor-core recurrence (one batched tcgen05 GEMM and one
- * gate kernel per timestep) wherever the shape allows it.  In mode 1 the library itself switches to
- * the tensor-core recurrence for large batches (many sequences x many units), where it is faster. */
+/* Which recurrence kernels run:
+ *   0  one launch per timestep;
+ *   1  persistent kernels, the library chooses the exchange between the blocks of a group (default):
+ *      thread-block clusters with transaction barriers in distributed shared memory for as many work
+ *      items as fit side by side, the remaining sequences through L2 on the SMs the clusters leave
+ *      free; for large batches (many sequences x many units) the tensor-core recurrence of mode 3;
+ *   2  persistent kernels, every group as a cluster where a group fits one (128 or 256 units per
+ *      direction), through L2 otherwise;
+ *   3  tensor-core recurrence (one batched tcgen05 GEMM and one gate kernel per timestep) wherever
+ *      the shape allows it;
+ *   4  persistent kernels, every exchange through L2. */
 int b2_lstm_set_recurrence_mode(b2_lstm *layer, int mode);
 /* Waits for the work enqueued on `stream` and reports what the layer's kernels recorded:
  * B2_ERR_STEP_TIMEOUT if a persistent kernel gave up a bounded wait, else B2_OK. */

@@ -167,10 +167,11 @@ int lstm_backward_tc(const LstmShape &s, const LstmBuffers &bf, const TcRecBuffe
 bool persistent_geometry(int els, int *JB);   // hidden units per block of the register-resident geometry
 size_t lstm_persistent_xchg_words(int els, int P, int D);
 int persistent_ps(int els, int P, int D, bool use_cluster);   // sequences per work item for a shape (0: no persistent kernel)
-// use_cluster: groups of <= 8 blocks exchange through distributed shared memory (thread-block clusters)
-int lstm_persistent(bool backward, bool use_cluster, const LstmShape &s, const LstmBuffers &b, const float *w, float *y,
+// transport: 0 = the blocks of a group exchange through L2; 1 = groups of <= 8 blocks run as thread-block
+// clusters and exchange through distributed shared memory; 2 = the layout a cost model prefers (clusters for as
+// many items as fit side by side, the remaining sequences through L2 on the SMs the clusters leave free)
+int lstm_persistent(bool backward, int transport, const LstmShape &s, const LstmBuffers &b, const float *w, float *y,
                     const float *dy, unsigned long long *xchg, int *status, unsigned *tag_next, cudaStream_t st);
-
 int lstm_selftest_bounded_wait(int *status_out, int *gave_up, cudaStream_t st);
 
 // offsets inside the (b)lstm weight vector

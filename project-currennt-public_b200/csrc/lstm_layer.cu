@@ -111,7 +111,7 @@ int LstmLayerImpl::forward(const float *w, const float *x, float *y, cudaStream_
             B2_TRY(ensure_tcrec());
             rc = lstm_forward_tc(s, bufs, tcrec, w, y, status_dev, st);
         } else if (recurrence_mode >= 1) {
-            rc = lstm_persistent(false, recurrence_mode == 2, s, bufs, w, y, nullptr, xchg, status_dev, &tag_next, st);
+            rc = lstm_persistent(false, persistent_transport(), s, bufs, w, y, nullptr, xchg, status_dev, &tag_next, st);
         }
         if (rc == 1) rc = lstm_forward_stepwise(s, bufs, w, y, st);
         B2_TRY(rc);
@@ -132,7 +132,7 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
         int rc = 1;
         if (tcrec_used) rc = lstm_backward_tc(s, bufs, tcrec, w, dy, status_dev, st);
         else if (recurrence_mode >= 1)
-            rc = lstm_persistent(true, recurrence_mode == 2, s, bufs, w, nullptr, dy, xchg, status_dev, &tag_next, st);
+            rc = lstm_persistent(true, persistent_transport(), s, bufs, w, nullptr, dy, xchg, status_dev, &tag_next, st);
         if (rc == 1) rc = lstm_backward_stepwise(s, bufs, w, dy, st);
         B2_TRY(rc);
     }

@@ -24,6 +24,8 @@ struct LstmLayerImpl {
     unsigned tag_next = 1;
     // tensor-core recurrence (large batches): hi/lo buffers, allocated on first use
     TcRecBuffers tcrec{};
+    // recurrence mode 1 lets the library choose the exchange, 2 forces clusters, 4 forces L2
+    int persistent_transport() const { return recurrence_mode == 2 ? 1 : (recurrence_mode == 4 ? 0 : 2); }
     bool tcrec_used = false;      // this fraction's forward sweep ran on the tensor-core recurrence
     bool want_tc_recurrence() const;
     int ensure_tcrec();

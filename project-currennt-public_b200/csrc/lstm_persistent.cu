@@ -168,7 +168,8 @@ struct PersistArgs {
     u64 *xchg;         // exchange buffers, per slot (L2 transport)
     int *status;       // 0 ok, else an error code
     unsigned tag_base;
-    int n_items;       // D * ceil(P / PS)
+    int n_items;       // D * ceil((p_hi - p_lo) / PS)
+    int p_lo, p_hi;    // the sequences this launch handles: items cover p_lo .. p_hi-1 in slices of PS
 };
 
 template <int ELS, int JB, int PS>
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
     float wreg[4][KPT];
     int cur_d = -1;
     for (int item = slot; item < a.n_items; item += nslots) {
-        const int d = item % D, p0 = (item / D) * PS, seq = item / nslots;
+        const int d = item % D, p0 = a.p_lo + (item / D) * PS, seq = item / nslots;
         if (d != cur_d) {
             // W_rec[gate][d][j0+jj][k] from the source-major copy [d][k][gate][j] (coalesced over j)
             const float *wt = a.bf.wrecT + (size_t)d * ELS * 4 * ELS;
@@ -283,7 +284,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
                 mode[ci] = 2;
                 if (c < CELLS) {
                     const int pg = p0 + c / JB;
-                    if (pg < P) {
+                    if (pg < a.p_hi) {
                         const size_t f = (size_t)t * P + pg;
                         const float *ap = a.bf.acts + f * 4 * ls + d * ELS + j0 + (c % JB);
 #pragma unroll
@@ -486,7 +487,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
     float wreg[4][RPT];
     int cur_d = -1;
     for (int item = slot; item < a.n_items; item += nslots) {
-        const int d = item % D, p0 = (item / D) * PS, seq = item / nslots;
+        const int d = item % D, p0 = a.p_lo + (item / D) * PS, seq = item / nslots;
         if (d != cur_d) {
             // W_rec[gate][d][j0+jj][k], row = gate*JB + jj, this thread's columns k = 4*kq .. 4*kq+3
 #pragma unroll
@@ -529,7 +530,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
                 cpv[ci] = 0.0f;
                 if (c < CELLS) {
                     const int pg = p0 + c / JB;
-                    if (pg < P) {
+                    if (pg < a.p_hi) {
                         const size_t f = (size_t)t * P + pg;
                         const int u = d * ELS + j0 + (c % JB);
                         mode[ci] = (t >= a.sh.Tmin && a.bf.pat[f] == PAT_NONE) ? 1 : 0;
@@ -881,35 +882,114 @@ int lstm_selftest_bounded_wait(int *status_out, int *gave_up, cudaStream_t st) {
     return B2_OK;
 }
 
-// returns B2_OK, an error, or 1 when this shape has no persistent kernel (caller uses the stepwise one)
-int lstm_persistent(bool backward, bool use_cluster, const LstmShape &s, const LstmBuffers &b, const float *w, float *y,
+namespace {
+// one launch over the sequences p_lo .. p_hi-1 with PS sequences per work item
+int run_part(bool backward, bool use_cluster, PersistArgs a, int els, int PS, int p_lo, int p_hi, cudaStream_t st, int *ips) {
+    a.p_lo = p_lo; a.p_hi = p_hi;
+    a.n_items = a.sh.D * ((p_hi - p_lo + PS - 1) / PS);
+    int rc = 1;
+#define CASE_PS(E, J, Q) \
+    case Q: rc = launch<E, J, Q>(backward, use_cluster, a, st, ips); break;
+#define CASE(E, J, MORE)                                         \
+    case E:                                                      \
+        switch (PS) {                                            \
+            CASE_PS(E, J, 1) CASE_PS(E, J, 4) CASE_PS(E, J, 8) MORE \
+            default: return 1;                                   \
+        }                                                        \
+        break;
+    switch (els) {
+        CASE(1024, 8, )
+        CASE(512, 16, CASE_PS(512, 16, 16))
+        CASE(256, 32, CASE_PS(256, 32, 2) CASE_PS(256, 32, 16))
+        CASE(128, 64, CASE_PS(128, 64, 2) CASE_PS(128, 64, 16))
+        default: return 1;
+    }
+#undef CASE
+#undef CASE_PS
+    return rc;
+}
+
+// second stream for the part of a sweep that runs beside the cluster launch
+cudaStream_t g_aux_stream = nullptr;
+cudaEvent_t g_fork = nullptr, g_join = nullptr;
+int ensure_aux() {
+    if (g_aux_stream) return B2_OK;
+    B2_CUDA(cudaStreamCreateWithFlags(&g_aux_stream, cudaStreamNonBlocking));
+    B2_CUDA(cudaEventCreateWithFlags(&g_fork, cudaEventDisableTiming));
+    B2_CUDA(cudaEventCreateWithFlags(&g_join, cudaEventDisableTiming));
+    return B2_OK;
+}
+}  // namespace
+
+// How a sweep is laid out (measured per-step costs on B200: exchange through L2 1.4 us + 0.27 us per
+// sequence of an item; through the cluster's shared memory 0.8 us + 0.29 us per sequence, but only as many
+// groups run as clusters as fit side by side):
+//   L2:      every item through L2, PS as persistent_ps picks it
+//   CLUSTER: every item as a cluster
+//   MIXED:   as many 4-sequence items as there are cluster slots run as clusters; the remaining sequences
+//            run beside them, on the SMs the clusters leave free, as 2- or 4-sequence items through L2
+struct SweepPlan { int kind; int ps_main; int split; int ps_rest; };
+enum { PLAN_L2 = 0, PLAN_CLUSTER = 1, PLAN_MIXED = 2 };
+static SweepPlan plan_sweep(int els, int P, int D, int transport) {
+    SweepPlan pl{PLAN_L2, persistent_ps(els, P, D, false), P, 0};
+    int JB;
+    if (!persistent_geometry(els, &JB)) return pl;
+    const int G = els / JB;
+    const int C = G <= 8 ? persistent_cluster_slots(els) : 0;
+    if (transport == 0 || C < 1) return pl;
+    if (transport == 1) {   // clusters for everything (more than one pass if they do not fit)
+        pl.kind = PLAN_CLUSTER;
+        pl.ps_main = persistent_ps(els, P, D, true);
+        return pl;
+    }
+    if (P == 1) return pl;
+    const int slots = num_sms() / G > 0 ? num_sms() / G : 1;
+    const int items_l2 = D * ((P + pl.ps_main - 1) / pl.ps_main);
+    double best = ((items_l2 + slots - 1) / slots) * (1.4 + 0.27 * pl.ps_main);
+    for (int ps = 4; ps <= 16; ps *= 2)
+        if (D * ((P + ps - 1) / ps) <= C) {
+            const double t = 0.8 + 0.29 * ps;
+            if (t < best) { best = t; pl = SweepPlan{PLAN_CLUSTER, ps, P, 0}; }
+            break;
+        }
+    const int slices = C / D;                       // 4-sequence cluster items per direction
+    const int rest = P - 4 * slices;
+    if (slices >= 1 && rest > 0) {
+        const int free_sms = num_sms() - slices * D * G;
+        for (int pr = 2; pr <= 4; pr *= 2)
+            if (D * ((rest + pr - 1) / pr) * G <= free_sms) {
+                const double t = (0.8 + 0.29 * 4 > 1.4 + 0.27 * pr) ? 0.8 + 0.29 * 4 : 1.4 + 0.27 * pr;
+                if (t < best) { best = t; pl = SweepPlan{PLAN_MIXED, 4, 4 * slices, pr}; }
+                break;
+            }
+    }
+    return pl;
+}
+
+// returns B2_OK, an error, or 1 when this shape has no persistent kernel (caller uses the stepwise one).
+// transport: 0 exchange through L2, 1 thread-block clusters, 2 whichever layout the cost model prefers
+int lstm_persistent(bool backward, int transport, const LstmShape &s, const LstmBuffers &b, const float *w, float *y,
                     const float *dy, unsigned long long *xchg, int *status, unsigned *tag_next, cudaStream_t st) {
     int JB;
     if (!persistent_geometry(s.els, &JB) || !xchg) return 1;
     PersistArgs a;
     a.sh = s; a.bf = b; a.w = w; a.y = y; a.dy = dy; a.xchg = xchg; a.status = status;
     a.tag_base = *tag_next;
-    const int PS = persistent_ps(s.els, s.P, s.D, use_cluster);
-    a.n_items = s.D * ((s.P + PS - 1) / PS);
-    int ips = 1, rc = 1;
-#define CASE_PS(E, J, Q) \
-    case Q: rc = launch<E, J, Q>(backward, use_cluster, a, st, &ips); break;
-#define CASE(E, J, WITH16)                                       \
-    case E:                                                      \
-        switch (PS) {                                            \
-            CASE_PS(E, J, 1) CASE_PS(E, J, 4) CASE_PS(E, J, 8) WITH16 \
-            default: return 1;                                   \
-        }                                                        \
-        break;
-    switch (s.els) {
-        CASE(1024, 8, )
-        CASE(512, 16, CASE_PS(512, 16, 16))
-        CASE(256, 32, CASE_PS(256, 32, 16))
-        CASE(128, 64, CASE_PS(128, 64, 16))
-        default: return 1;
+    const SweepPlan pl = plan_sweep(s.els, s.P, s.D, transport);
+    int ips = 1, rc;
+    if (pl.kind == PLAN_MIXED) {
+        B2_TRY(ensure_aux());
+        B2_CUDA(cudaEventRecord(g_fork, st));
+        B2_CUDA(cudaStreamWaitEvent(g_aux_stream, g_fork, 0));
+        int ips_cl = 1;
+        rc = run_part(backward, true, a, s.els, pl.ps_main, 0, pl.split, st, &ips_cl);
+        if (rc != B2_OK) return rc;
+        rc = run_part(backward, false, a, s.els, pl.ps_rest, pl.split, s.P, g_aux_stream, &ips);
+        B2_CUDA(cudaEventRecord(g_join, g_aux_stream));
+        B2_CUDA(cudaStreamWaitEvent(st, g_join, 0));
+    } else {
+        rc = run_part(backward, pl.kind == PLAN_CLUSTER, a, s.els, pl.ps_main, 0, s.P, st, &ips);
     }
-#undef CASE
-#undef CASE_PS
     if (rc == B2_OK) *tag_next += (unsigned)ips * (unsigned)(s.T + 1) + 1u;
     return rc;
 }

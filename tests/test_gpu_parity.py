@@ -13,9 +13,9 @@ from oracle import ref_available
 pytestmark = pytest.mark.gpu
 
 VARIANTS = [dict(recurrence=0, ffma=1), dict(recurrence=1, ffma=1), dict(recurrence=1, ffma=0), dict(recurrence=2, ffma=0),
-            dict(recurrence=3, ffma=0), dict(recurrence=0, ffma=0)]
+            dict(recurrence=3, ffma=0), dict(recurrence=0, ffma=0), dict(recurrence=4, ffma=0)]
 VARIANT_IDS = ["stepwise-ffma", "persistent-ffma", "persistent-tensor", "persistent_cluster-tensor", "tensor_recurrence-tensor",
-               "stepwise-tensor"]
+               "stepwise-tensor", "persistent_l2-tensor"]
 
 
 def run_gpu(layers, P, lens, x, tg, weights, variant, lr=1e-4, mom=0.9, maxT=None):
@@ -116,8 +116,10 @@ def test_config_layer_sizes_reduced_frames(cfg, P, scale, variant):
     parity.compare_run(wl["layers"], got, want, "cfg%d reduced" % cfg, lstm_pad_zero_lens=wl["lens"])
 
 
-@pytest.mark.parametrize("variant", VARIANTS[1:5], ids=VARIANT_IDS[1:5])
+@pytest.mark.parametrize("variant", VARIANTS[1:5] + VARIANTS[6:], ids=VARIANT_IDS[1:5] + VARIANT_IDS[6:])
 @pytest.mark.parametrize("ls,bi,P,lens", [(2048, 1, 5, [12, 12, 7, 3, 12]), (1024, 0, 1, [9]), (256, 1, 9, [14] * 9),
+                                          (256, 0, 1, [11]), (128, 0, 1, [12]), (512, 1, 1, [8]),
+                                          (512, 1, 32, [9] * 30 + [5, 2]), (512, 1, 38, [6] * 37 + [3]), (256, 1, 34, [7] * 34),
                                           (512, 1, 2, [6, 11]), (256, 0, 7, [10, 9, 8, 7, 6, 5, 4]),
                                           (512, 1, 40, [7] * 20 + [5] * 19 + [2]), (512, 1, 83, [5] * 80 + [3, 2, 1]),
                                           (1024, 1, 9, [6] * 8 + [4]), (1024, 1, 21, [5] * 21), (256, 1, 150, [3] * 150)])
