@@ -272,27 +272,42 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
         }
 
         bool dead = false;
+        // pre-activations and padding flags are fetched ONE STEP AHEAD: they come from HBM (the projection of a
+        // long fraction does not fit L2) and a step is shorter than that latency
+        float a4n[CPT][4];
+        int moden[CPT];  // 0 compute, 1 padding frame, 2 sequence slot beyond the launch's range
+        auto fetch = [&](int sn) {
+            const int tn = d ? T - 1 - sn : sn;
+#pragma unroll
+            for (int ci = 0; ci < CPT; ++ci) {
+                const int c = tid + ci * NT;
+                moden[ci] = 2;
+                if (c < CELLS) {
+                    const int pg = p0 + c / JB;
+                    if (pg < a.p_hi) {
+                        const size_t f = (size_t)tn * P + pg;
+                        const float *ap = a.bf.acts + f * 4 * ls + d * ELS + j0 + (c % JB);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) a4n[ci][q] = ap[(size_t)q * ls];
+                        moden[ci] = (tn >= a.sh.Tmin && a.bf.pat[f] == PAT_NONE) ? 1 : 0;
+                    }
+                }
+            }
+        };
+        if (T > 0) fetch(0);
         for (int s = 0; s < T; ++s) {
             const int t = d ? T - 1 - s : s;
             const bool first = (s == 0);
             // 1. pre-activations of this step for the block's cells (independent of the recurrence)
             float a4[CPT][4];
-            int mode[CPT];  // 0 compute, 1 padding frame, 2 sequence slot beyond P
+            int mode[CPT];
 #pragma unroll
             for (int ci = 0; ci < CPT; ++ci) {
-                const int c = tid + ci * NT;
-                mode[ci] = 2;
-                if (c < CELLS) {
-                    const int pg = p0 + c / JB;
-                    if (pg < a.p_hi) {
-                        const size_t f = (size_t)t * P + pg;
-                        const float *ap = a.bf.acts + f * 4 * ls + d * ELS + j0 + (c % JB);
+                mode[ci] = moden[ci];
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) a4[ci][q] = ap[(size_t)q * ls];
-                        mode[ci] = (t >= a.sh.Tmin && a.bf.pat[f] == PAT_NONE) ? 1 : 0;
-                    }
-                }
+                for (int q = 0; q < 4; ++q) a4[ci][q] = a4n[ci][q];
             }
+            if (s + 1 < T) fetch(s + 1);
             if constexpr (CL) {
                 // this step's h of all G blocks will arrive in buffer s&1 (the last step publishes nothing)
                 if (tid == 0 && s + 1 < T) mbar_expect_tx(smem_addr(&hbar[s & 1]), (uint32_t)(ELS * PS * sizeof(float)));
