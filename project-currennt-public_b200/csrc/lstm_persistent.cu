@@ -276,6 +276,23 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
         // long fraction does not fit L2) and a step is shorter than that latency
         float a4n[CPT][4];
         int moden[CPT];  // 0 compute, 1 padding frame, 2 sequence slot beyond the launch's range
+        // Padding frames (pattern type NONE) trail a sequence, as the data set writes them: the first one is
+        // found once per item by bisection, so that the step loop does not wait on a pattern-type load
+        int seqlen[CPT];
+#pragma unroll
+        for (int ci = 0; ci < CPT; ++ci) {
+            const int c = tid + ci * NT;
+            seqlen[ci] = T;
+            if (c < CELLS && p0 + c / JB < a.p_hi && a.sh.Tmin < T) {
+                const int pg = p0 + c / JB;
+                int lo = a.sh.Tmin, hi = T;   // frames below Tmin are real for every sequence
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (a.bf.pat[(size_t)mid * P + pg] == PAT_NONE) hi = mid; else lo = mid + 1;
+                }
+                seqlen[ci] = lo;
+            }
+        }
         auto fetch = [&](int sn) {
             const int tn = d ? T - 1 - sn : sn;
 #pragma unroll
@@ -289,7 +306,7 @@ __global__ void __launch_bounds__(NT, 1) lstm_fwd_persistent_kernel(PersistArgs 
                         const float *ap = a.bf.acts + f * 4 * ls + d * ELS + j0 + (c % JB);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) a4n[ci][q] = ap[(size_t)q * ls];
-                        moden[ci] = (tn >= a.sh.Tmin && a.bf.pat[f] == PAT_NONE) ? 1 : 0;
+                        moden[ci] = tn >= seqlen[ci] ? 1 : 0;
                     }
                 }
             }
