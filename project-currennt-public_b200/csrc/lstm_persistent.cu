@@ -487,6 +487,9 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
     constexpr int G = Gm::G, CELLS = Gm::CELLS, CPT = Gm::CPT, PC = Gm::PC;
     constexpr int KQ = Gm::KQ, RSPLIT = Gm::RSPLIT, RPT = Gm::RPT, NPART = Gm::NPART;
     constexpr int SRC_PER_PART = (G + NPART - 1) / NPART;
+    // cluster transport with one thread per unit: the PS partial sums of a unit travel as 16-byte stores, the
+    // receive buffers then hold [src][unit][sequence] instead of [src][sequence][unit]
+    constexpr bool VEC = CL && ELS == NT && PS % 4 == 0;
     // partial sums received, [src][cell]; with clusters the peers write them directly, double-buffered
     float *pe_all = smem_dyn;
     float *pe2 = pe_all + (CL ? 2 : 1) * Gm::BWD_PE;   // first-stage sums, [part][cell]
@@ -641,9 +644,9 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
                     if (!firstCall) {
                         if constexpr (CELLS <= NT) {
 #pragma unroll
-                            for (int q = 0; q < NPART; ++q) e += pe2[q * CELLS + c];
+                            for (int q = 0; q < NPART; ++q) e += pe2[q * CELLS + (VEC ? jj * PS + p : c)];
                         } else {
-                            for (int src = 0; src < G; ++src) e += pe[src * CELLS + c];
+                            for (int src = 0; src < G; ++src) e += pe[src * CELLS + (VEC ? jj * PS + p : c)];
                         }
                     }
                     const float ni = a4[ci][0], ig = a4[ci][1], fg = a4[ci][2], og = a4[ci][3];
@@ -716,15 +719,32 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
             }
             // combine the row-splits and send with consecutive threads on consecutive units (coalesced)
             __syncthreads();
+            if constexpr (VEC) {
+                // thread = unit k; its PS sums go to the owner of k in 16-byte pieces
+                float v[PS];
 #pragma unroll
-            for (int q0 = 0; q0 < (ELS * PS + NT - 1) / NT; ++q0) {
-                const int i = tid + q0 * NT;
-                if ((ELS * PS) % NT != 0 && i >= ELS * PS) break;
-                const int k = i % ELS, p = i / ELS;
-                float v = 0.0f;
+                for (int p = 0; p < PS; ++p) {
+                    v[p] = 0.0f;
 #pragma unroll
-                for (int q = 0; q < RSPLIT; ++q) v += redb[(size_t)(q * PS + p) * ELS + k];
-                send(k, p, v);
+                    for (int q = 0; q < RSPLIT; ++q) v[p] += redb[(size_t)(q * PS + p) * ELS + tid];
+                }
+                const uint32_t owner = (uint32_t)(tid / JB);
+                const uint32_t rbar = map_to_rank(smem_addr(&ebar[s & 1]), owner);
+                const uint32_t la = smem_addr(pe_all + ((s & 1) * G + g) * CELLS + (tid % JB) * PS);
+#pragma unroll
+                for (int p4 = 0; p4 < PS / 4; ++p4)
+                    st_async_v4(map_to_rank(la + 16u * p4, owner), make_float4(v[4 * p4], v[4 * p4 + 1], v[4 * p4 + 2], v[4 * p4 + 3]), rbar);
+            } else {
+#pragma unroll
+                for (int q0 = 0; q0 < (ELS * PS + NT - 1) / NT; ++q0) {
+                    const int i = tid + q0 * NT;
+                    if ((ELS * PS) % NT != 0 && i >= ELS * PS) break;
+                    const int k = i % ELS, p = i / ELS;
+                    float v = 0.0f;
+#pragma unroll
+                    for (int q = 0; q < RSPLIT; ++q) v += redb[(size_t)(q * PS + p) * ELS + k];
+                    send(k, p, v);
+                }
             }
             store_deltas();
         }
