@@ -551,33 +551,66 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
         }
 
         bool dead = false;
+        // the first padding frame of each of this thread's sequences (see the forward kernel)
+        int seqlen[CPT];
+#pragma unroll
+        for (int ci = 0; ci < CPT; ++ci) {
+            const int c = tid + ci * NT;
+            seqlen[ci] = T;
+            if (c < CELLS && p0 + c / JB < a.p_hi && a.sh.Tmin < T) {
+                const int pg = p0 + c / JB;
+                int lo = a.sh.Tmin, hi = T;
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (a.bf.pat[(size_t)mid * P + pg] == PAT_NONE) hi = mid; else lo = mid + 1;
+                }
+                seqlen[ci] = lo;
+            }
+        }
+        // everything a step needs from HBM is independent of the recurrence and is fetched one step ahead
+        float e_n[CPT], a4n[CPT][4], cpvn[CPT], cc_first[CPT];
+        int moden[CPT];
+        auto fetch = [&](int sn) {
+            const int tn = d ? sn : T - 1 - sn;
+            const int prevn = d ? tn + 1 : tn - 1;
+#pragma unroll
+            for (int ci = 0; ci < CPT; ++ci) {
+                const int c = tid + ci * NT;
+                moden[ci] = 2;
+                cpvn[ci] = 0.0f;
+                if (c < CELLS) {
+                    const int pg = p0 + c / JB;
+                    if (pg < a.p_hi) {
+                        const size_t f = (size_t)tn * P + pg;
+                        const int u = d * ELS + j0 + (c % JB);
+                        moden[ci] = tn >= seqlen[ci] ? 1 : 0;
+                        e_n[ci] = a.dy[f * ls + u];
+                        const float *ap = a.bf.acts + f * 4 * ls + u;
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) a4n[ci][q] = ap[(size_t)q * ls];
+                        if (sn == 0) cc_first[ci] = a.bf.cells[f * ls + u];
+                        if (sn != T - 1) cpvn[ci] = a.bf.cells[((size_t)prevn * P + pg) * ls + u];
+                    }
+                }
+            }
+        };
+        if (T > 0) fetch(0);
         for (int s = 0; s < T; ++s) {
             const int t = d ? s : T - 1 - s;
-            const int prevc = d ? t + 1 : t - 1;
             const bool firstCall = (s == 0), lastCall = (s == T - 1);
-            // 1. everything this step needs from HBM (independent of the recurrence)
+            // 1. this step's inputs (fetched during the step before), then the next step's fetch
             float e_in[CPT], a4[CPT][4], cc[CPT], cpv[CPT];
             int mode[CPT];
 #pragma unroll
             for (int ci = 0; ci < CPT; ++ci) {
-                const int c = tid + ci * NT;
-                mode[ci] = 2;
-                cpv[ci] = 0.0f;
-                if (c < CELLS) {
-                    const int pg = p0 + c / JB;
-                    if (pg < a.p_hi) {
-                        const size_t f = (size_t)t * P + pg;
-                        const int u = d * ELS + j0 + (c % JB);
-                        mode[ci] = (t >= a.sh.Tmin && a.bf.pat[f] == PAT_NONE) ? 1 : 0;
-                        e_in[ci] = a.dy[f * ls + u];
-                        const float *ap = a.bf.acts + f * 4 * ls + u;
+                mode[ci] = moden[ci];
+                e_in[ci] = e_n[ci];
+                cpv[ci] = cpvn[ci];
+                cc[ci] = firstCall ? cc_first[ci] : c_keep[ci];
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) a4[ci][q] = ap[(size_t)q * ls];
-                        cc[ci] = firstCall ? a.bf.cells[f * ls + u] : c_keep[ci];
-                        if (!lastCall) cpv[ci] = a.bf.cells[((size_t)prevc * P + pg) * ls + u];
-                    }
-                }
+                for (int q = 0; q < 4; ++q) a4[ci][q] = a4n[ci][q];
             }
+            if (s + 1 < T) fetch(s + 1);
             if constexpr (CL) {
                 // this step's partial sums of all G blocks will arrive in buffer s&1 (the last step sends nothing)
                 if (tid == 0 && !lastCall) mbar_expect_tx(smem_addr(&ebar[s & 1]), (uint32_t)(G * CELLS * sizeof(float)));
