@@ -338,11 +338,11 @@ def main():
         # DRAM bytes per launch of the dominant kernel, from the ncu capture summarised in
         # profiles/lstm_persistent_kernels_cfg1_quarter_frames.md (bytes per unit and frame slot,
         # scaled by the units x frame slots of one launch; traffic grows in proportion to the frames)
-        per_cell = {"lstm_fwd_recurrence": 28.7, "lstm_bwd_recurrence": 34.2}.get(top)
+        per_cell = {"lstm_fwd_recurrence": 26.1, "lstm_bwd_recurrence": 32.2}.get(top)
         lstm_sizes = [l["size"] for l in layers if l["type"] in ("lstm", "blstm")]
         if per_cell and lstm_sizes and args.workload == "cfg1" and args.recurrence == 1 and not args.ffma:
             roof["traffic"] = per_cell * (sum(lstm_sizes) / len(lstm_sizes)) * T * P
-            roof["traffic_note"] = "bytes per launch (one layer's sweep), ncu dram__bytes scaled from a quarter-size capture"
+            roof["traffic_note"] = "bytes per sweep of one layer (its two side-by-side launches), ncu dram__bytes scaled from a quarter-size capture"
             roof["launches"] = len(lstm_sizes)
         else:
             roof["traffic"] = None
