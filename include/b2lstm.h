@@ -217,8 +217,9 @@ int b2_net_get_output_errors(b2_net *net, int layer, float *host_out);
 int b2_net_synchronize(b2_net *net);
 /* The stream all of the net's work is ordered on (a cudaStream_t). */
 b2_stream b2_net_stream(b2_net *net);
-/* 0 = stepwise recurrence kernels, 1 = persistent (default), 2 = persistent with cluster exchange;
- * applies to every (b)lstm layer (see b2_lstm_set_recurrence_mode). */
+/* The recurrence mode of every (b)lstm layer, values as for b2_lstm_set_recurrence_mode: 0 stepwise,
+ * 1 persistent with the exchange the library chooses (default), 2 clusters, 3 tensor-core
+ * recurrence, 4 L2 only. */
 int b2_net_set_recurrence_mode(b2_net *net, int mode);
 /* Non-zero forces the FFMA GEMM everywhere (the tensor-core GEMM is the default). */
 int b2_net_set_force_ffma(b2_net *net, int on);
