@@ -994,9 +994,10 @@ int run_part(bool backward, bool use_cluster, PersistArgs a, int els, int PS, in
     return rc;
 }
 
-// second stream for the part of a sweep that runs beside the cluster launch
-cudaStream_t g_aux_stream = nullptr;
-cudaEvent_t g_fork = nullptr, g_join = nullptr;
+// second stream for the part of a sweep that runs beside the cluster launch; one per host thread, so that
+// handles driven from different threads do not share the fork / join events
+thread_local cudaStream_t g_aux_stream = nullptr;
+thread_local cudaEvent_t g_fork = nullptr, g_join = nullptr;
 int ensure_aux() {
     if (g_aux_stream) return B2_OK;
     B2_CUDA(cudaStreamCreateWithFlags(&g_aux_stream, cudaStreamNonBlocking));
