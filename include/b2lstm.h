@@ -93,7 +93,8 @@ size_t b2_lstm_num_weights(const b2_lstm_desc *desc);
 int b2_lstm_create(const b2_lstm_desc *desc, b2_lstm **out);
 void b2_lstm_destroy(b2_lstm *layer);
 /* LstmLayer::loadSequences (LstmLayer.cu:1489-1533, Layer.cu:254-305): take over the current
- * fraction's shape.  pat_types_dev: device char[cur_max_len * P]. */
+ * fraction's shape.  pat_types_dev: device char[cur_max_len * P]; padding frames (type 0) must trail
+ * their sequence, as data_sets::DataSet writes them. */
 int b2_lstm_load_sequences(b2_lstm *layer, int cur_max_len, int cur_min_len, const char *pat_types_dev);
 /* LstmLayer::computeForwardPass (LstmLayer.cu:1744-1949).
  * weights_dev: b2_lstm_num_weights floats; x_dev: prev_size x (T*P) = precedingLayer().outputs();
