@@ -204,11 +204,17 @@ int LstmLayer::computeBackwardPass(int) {
 SsePostOutputLayer::~SsePostOutputLayer() {
     cudaFree(lossDev_);
     cudaFree(lossWs_);
+    if (lossPinned_) cudaFreeHost(lossPinned_);
+    if (lossReady_) cudaEventDestroy(lossReady_);
 }
 int SsePostOutputLayer::init() {
     B2_CUDA(cudaMalloc(&lossDev_, sizeof(double)));
     B2_CUDA(cudaMalloc(&lossWs_, 1024 * sizeof(double)));
     B2_CUDA(cudaMemset(lossDev_, 0, sizeof(double)));
+    B2_CUDA(cudaMallocHost(&lossPinned_, 2 * sizeof(double)));
+    lossPinned_[0] = lossPinned_[1] = 0.0;
+    B2_CUDA(cudaEventCreateWithFlags(&lossReady_, cudaEventDisableTiming));
+    B2_CUDA(cudaEventRecord(lossReady_, net_.stream));
     return B2_OK;
 }
 int SsePostOutputLayer::loadSequences(const Fraction &f, int nnState) {
@@ -221,10 +227,17 @@ int SsePostOutputLayer::calculateError(double *hostError) {
         ProfScope ps(net_, "sse_loss");
         B2_TRY(sse_loss(lossDev_, prev_->outputs(), targets_, pat_, size_, (size_t)curMax_ * P_, lossWs_, net_.stream));
     }
-    if (hostError) {
-        B2_CUDA(cudaMemcpyAsync(hostError, lossDev_, sizeof(double), cudaMemcpyDeviceToHost, net_.stream));
-        B2_CUDA(cudaStreamSynchronize(net_.stream));
-    }
+    // the error goes to a pinned slot at once, with an event behind it: a reader then waits for the forward
+    // pass only, not for whatever the stream holds after it (b2_net_read_error)
+    lossSlot_ ^= 1;
+    B2_CUDA(cudaMemcpyAsync(lossPinned_ + lossSlot_, lossDev_, sizeof(double), cudaMemcpyDeviceToHost, net_.stream));
+    B2_CUDA(cudaEventRecord(lossReady_, net_.stream));
+    if (hostError) B2_TRY(readError(hostError));
+    return B2_OK;
+}
+int SsePostOutputLayer::readError(double *hostError) {
+    B2_CUDA(cudaEventSynchronize(lossReady_));
+    *hostError = lossPinned_[lossSlot_];
     return B2_OK;
 }
 int SsePostOutputLayer::computeBackwardPass(int) {
@@ -755,7 +768,7 @@ int b2_net_train_step_prefetched(b2_net *n, float lr, float mom, double *error) 
     B2_TRY(n->net.updateWeights(lr, mom));
     if (error) {
         SsePostOutputLayer *post = dynamic_cast<SsePostOutputLayer *>(n->net.layers.back().get());
-        B2_CUDA(cudaMemcpyAsync(error, post->lossDev(), sizeof(double), cudaMemcpyDeviceToHost, n->net.stream));
+        B2_TRY(post->readError(error));
         B2_CUDA(cudaStreamSynchronize(n->net.stream));
     }
     return B2_OK;
@@ -764,9 +777,7 @@ int b2_net_read_error(b2_net *n, double *error) {
     if (!n || !error) return B2_ERR_BAD_ARG;
     SsePostOutputLayer *post = dynamic_cast<SsePostOutputLayer *>(n->net.layers.back().get());
     if (!post) { set_error("the last layer is not a post-output layer"); return B2_ERR_STATE; }
-    B2_CUDA(cudaMemcpyAsync(error, post->lossDev(), sizeof(double), cudaMemcpyDeviceToHost, n->net.stream));
-    B2_CUDA(cudaStreamSynchronize(n->net.stream));
-    return B2_OK;
+    return post->readError(error);
 }
 int b2_net_train_step_dev(b2_net *n, int T, int nSeq, const int *lens, const float *in, const float *tg, float lr,
                           float mom) {

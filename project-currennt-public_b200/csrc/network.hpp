@@ -123,6 +123,7 @@ public:
     int computeForwardPass(int) override { return B2_OK; }
     int computeBackwardPass(int nnState) override;
     int calculateError(double *hostError);   // hostError == NULL: stay asynchronous
+    int readError(double *hostError);        // waits for the last calculateError only
     double *lossDev() { return lossDev_; }
     int init();
     ~SsePostOutputLayer() override;
@@ -130,6 +131,9 @@ public:
 private:
     const float *targets_ = nullptr;
     double *lossDev_ = nullptr, *lossWs_ = nullptr;
+    double *lossPinned_ = nullptr;   // two pinned slots, alternating
+    int lossSlot_ = 0;
+    cudaEvent_t lossReady_ = nullptr;
 };
 
 struct ProfileEntry {
