@@ -5,10 +5,14 @@
 
 A step is one pass of the hot path over one fraction of synthetic input: load -> forward through
 all layers -> SSE -> BPTT backward -> weight gradients -> [all-reduce] -> steepest-descent update.
-The default workload is configuration 1 (382 -> 2x feedforward_tanh 512 -> 2x blstm 256/direction
--> 187 -> sse, 32 parallel sequences of 300..1200 frames).  With N > 1 (launched by
-torch.distributed.run, one process per GPU) every rank processes its own fraction of that shape
-and the weight gradients are summed with NCCL before the update (weak scaling).
+The default workload is configuration 4 (382 -> 3x blstm 512/direction -> 187 -> sse, ONE fraction of
+256 parallel sequences of 600..1000 frames).  With N > 1 (launched by torch.distributed.run, one
+process per GPU) the same 256 sequences are dealt to the ranks in snake order, every rank processes
+its 256/N sequences and the weight gradients are summed with NCCL before the update (strong
+scaling: the job is the same at every N).  After the timed steps such a run checks itself: the
+weights must be bit-identical on all ranks, and the summed error and all-reduced gradients of the
+sharded first step must equal what rank 0 computes on the unsharded fraction.  The other
+configurations (--workload cfg0..cfg3) give every rank a fraction of its own (weak scaling).
 
 `value`  : real (unpadded) frames of all ranks per second, inputs already resident in HBM,
            timed with CUDA events on the library's stream, max over ranks.
@@ -28,6 +32,12 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "project-currennt-public_b200"))
+
+# (workload, phase, recurrence path) -> DRAM bytes per cell-step (one unit, one frame slot) measured with ncu
+TRAFFIC_BYTES_PER_CELL_STEP = {
+    ("cfg1", "lstm_fwd_recurrence", "persistent_ffma"): 26.1,
+    ("cfg1", "lstm_bwd_recurrence", "persistent_ffma"): 32.2,
+}
 
 METRIC = "blstm_train_step_frames_per_sec"
 UNIT = "frames/s"
@@ -113,21 +123,31 @@ def phase_work(layers, T, P, real_frames, count_padding=True):
     return w
 
 
+def scaling_of(args, world):
+    """cfg4 is ONE fraction of 256 sequences dealt to the ranks (strong scaling) unless --weak is given"""
+    return "strong" if (args.workload == "cfg4" and not args.weak) else "weak"
+
+
 def run_reference(args, rank, world):
     """Reference arm: the reference's own Cpu code on the host cores, bounded sample of the workload."""
     if rank != 0:
         return
-    os.environ.setdefault("OMP_NUM_THREADS", str(os.cpu_count() or 1))
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the reference arm uses every host core
+    # whatever the launcher set (the OpenMP runtime reads the variable when the library is loaded, below)
+    ncores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(ncores)
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     from oracle import OracleNet, ref_available
     from b2lstm import workloads
     cfg = int(args.workload.replace("cfg", ""))
     kind = "ref_omp" if ref_available(omp=True) else "port"
-    cores = (os.cpu_count() or 1) if kind == "ref_omp" else 1
+    cores = ncores if kind == "ref_omp" else 1
     # bounded sample: the configuration's layer sizes on P_s sequences of reduced length
     c = workloads.CONFIGS[cfg]
     P_s = min(c["P"], 8)
-    scale = args.cpu_scale
+    # frames of the sample as a share of the workload's sequence lengths: about one to two seconds of work per
+    # step for the OpenMP build of the reference on a few dozen cores
+    scale = args.cpu_scale if args.cpu_scale > 0 else {0: 1.0, 1: 0.05, 2: 0.01, 3: 0.02, 4: 0.06}[cfg]
 
     def one(scale):
         wl = workloads.build(cfg, scale_frames=scale, P=P_s)
@@ -142,10 +162,10 @@ def run_reference(args, rank, world):
         dt = time.perf_counter() - t0
         net.close()
         return int(wl["lens"].sum()), dt
-    frames, dt = one(scale)          # calibration doubles as warm-up
-    target = args.cpu_seconds / max(1, args.steps + args.warmup)
-    scale2 = min(1.0, max(scale, scale * target / max(dt, 1e-3)))
-    for _ in range(max(0, args.warmup - 1)):
+    # The sample is FIXED per workload (no calibration against the clock): the same frames at every N and in
+    # every run, so that the figure is comparable between runs.  One untimed pass warms the caches up.
+    scale2 = scale
+    for _ in range(max(1, args.warmup)):
         one(scale2)
     tot_f, tot_t = 0, 0.0
     for _ in range(args.steps):
@@ -157,12 +177,107 @@ def run_reference(args, rank, world):
         args.workload, P_s, int(c["len_hi"] * scale2), tot_f // max(1, args.steps), args.steps)
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1e3 * tot_t / max(1, args.steps), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workloads.CONFIGS[cfg]["name"], "sample": sample},
+            "scaling": scaling_of(args, world), "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workloads.CONFIGS[cfg]["name"], "sample": sample, "omp_threads": cores},
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "reference" if kind == "ref_omp" else "port",
                              "sample": sample},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def dp_correctness_record(net, wl, full, rank, world, dist, torch, args):
+    """What the data-parallel job computed, checked after the timed steps (N > 1).
+    (1) The weights of every layer are bit-identical on all ranks (byte-wise maximum == minimum over ranks).
+    (2) Strong scaling only: from fresh, identical weights every rank runs forward + backward on its shard (the
+        backward pass all-reduces the gradients); rank 0 then runs the UNSHARDED fraction on one GPU.  Summed
+        error: relative 1e-5.  Every gradient block: relative L2 and max-abs ratio 1e-4."""
+    import numpy as np
+    import b2lstm
+    rec = {"weights_identical_on_all_ranks": True}
+    for i in wl["weights"]:
+        w = torch.from_numpy(net.get_weights(i).view(np.int32).copy()).cuda()
+        hi, lo = w.clone(), w.clone()
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        if not bool(torch.equal(hi, lo)):
+            rec["weights_identical_on_all_ranks"] = False
+    if full is None:
+        return rec
+    for i, w in wl["weights"].items():
+        net.set_weights(i, w)
+    net.load_fraction(wl["lens"], wl["x"], wl["tg"])
+    err = net.dp_allreduce_scalar(net.forward())
+    net.backward()
+    net.synchronize()
+    grads = {i: net.weight_updates(i) for i in wl["weights"]}
+    dist.barrier()
+    if rank == 0:
+        layers = full["layers"]
+        one = b2lstm.Net(layers, full["P"], int(full["lens"].max()))
+        one.set_recurrence_mode(args.recurrence)
+        one.set_force_ffma(args.ffma)
+        for i, w in full["weights"].items():
+            one.set_weights(i, w)
+        one.load_fraction(full["lens"], full["x"], full["tg"])
+        err1 = one.forward()
+        one.backward()
+        one.synchronize()
+        worst_l2, worst_max = 0.0, 0.0
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import parity
+        for i in full["weights"]:
+            g1 = one.weight_updates(i).astype(np.float64)
+            g = grads[i].astype(np.float64)
+            for name, sl in parity.weight_blocks(layers, i).items():
+                a, b = g[sl], g1[sl]
+                nb = np.linalg.norm(b)
+                if nb > 0:
+                    worst_l2 = max(worst_l2, float(np.linalg.norm(a - b) / nb))
+                    worst_max = max(worst_max, float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)))
+        one.close()
+        rec.update({"error_sharded": err, "error_one_gpu": err1, "error_rel_diff": abs(err - err1) / max(abs(err1), 1e-30),
+                    "gradient_rel_l2_worst_block": worst_l2, "gradient_max_abs_ratio_worst_block": worst_max,
+                    "ok": bool(rec["weights_identical_on_all_ranks"] and abs(err - err1) <= 1e-5 * abs(err1)
+                               and worst_l2 <= 1e-4 and worst_max <= 1e-4)})
+    dist.barrier()
+    return rec
+
+
+def run_gemm_microbench(spec, iters, ffma):
+    """--gemm m,n,k,ta,tb: b2_matrix_multiply (the helpers::Matrix GEMM wrapper) on one shape, operand split kernels
+    inside the timed region, with the relative L2 error of 64 rows against float64.  ta/tb are the transpose flags
+    of the reference's Matrix::assignProduct on column-major operands: 1,0 = K-major x K-major (input projection
+    W^T X); 0,0 = MN-major x K-major (error back-projection W delta); 0,1 = MN-major x MN-major (weight gradient
+    X delta^T).  Prints one JSON line; it is a kernel figure for profiles/, not the benchmark value."""
+    import numpy as np
+    import torch
+    import b2lstm
+    m, n, k, ta, tb = [int(v) for v in spec.split(",")]
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(1)
+    A = torch.randn((k, m) if not ta else (m, k), device=dev, generator=g)
+    B = torch.randn((n, k) if not tb else (k, n), device=dev, generator=g)
+    Cm = torch.zeros((n, m), device=dev)
+    lda, ldb = (m if not ta else k), (k if not tb else n)
+
+    def run():
+        b2lstm.matrix_multiply(Cm, m, A, lda, ta, B, ldb, tb, m, n, k, accumulate=False, force_ffma=bool(ffma))
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    rows = min(m, 64)
+    want = ((A.T if not ta else A)[:rows].double() @ (B.T if not tb else B).double()).cpu().numpy()
+    got = Cm.T[:rows].double().cpu().numpy()
+    print(json.dumps({"gemm": {"m": m, "n": n, "k": k, "ta": ta, "tb": tb}, "kernel": "ffma" if ffma else "tcgen05_3xtf32",
+                      "ms": ms, "tflops": 2.0 * m * n * k / (ms * 1e-3) / 1e12,
+                      "rel_l2_err_vs_f64": float(np.linalg.norm(got - want) / np.linalg.norm(want))}), flush=True)
 
 
 def main():
@@ -171,16 +286,22 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b2lstm", choices=["b2lstm", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4"])
-    ap.add_argument("--strong", action="store_true", help="split the workload's sequences over the ranks (cfg4)")
+    ap.add_argument("--workload", default="cfg4", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--strong", action="store_true", help="accepted for compatibility: cfg4 is always split over the ranks")
+    ap.add_argument("--weak", action="store_true", help="cfg4: give every rank a full 256-sequence fraction of its own instead")
+    ap.add_argument("--no-check", action="store_true", help="N > 1: skip the correctness record after the timed steps")
     ap.add_argument("--recurrence", type=int, default=1)
     ap.add_argument("--ffma", type=int, default=0)
-    ap.add_argument("--cpu-seconds", type=float, default=20.0, help="budget of the CPU baseline sample")
-    ap.add_argument("--cpu-scale", type=float, default=0.02)
+    ap.add_argument("--cpu-scale", type=float, default=0.0,
+                    help="reference arm: frames of its sample as a share of the workload's lengths (0: the fixed per-workload value)")
     ap.add_argument("--frames-scale", type=float, default=1.0,
                     help="shorten every sequence by this factor (profiler captures only; such a line is not a bench value)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemm", default="", help="m,n,k,ta,tb: time b2_matrix_multiply on one shape instead of the train step")
     args = ap.parse_args()
+    if args.gemm:
+        run_gemm_microbench(args.gemm, max(1, args.steps), args.ffma)
+        return
     if args.frames_scale == 1.0:
         args.warmup = max(args.warmup, 3) if args.impl == "b2lstm" else max(args.warmup, 1)
 
@@ -205,8 +326,9 @@ def main():
 
     cfg = int(args.workload.replace("cfg", ""))
     c = workloads.CONFIGS[cfg]
-    if args.strong and world > 1:
-        full = workloads.build(cfg)
+    strong = scaling_of(args, world) == "strong"
+    if strong and world > 1:
+        full = workloads.build(cfg, scale_frames=args.frames_scale)
         from b2lstm import dp
         idx = dp.shard_indices(c["P"], rank, world)   # deal the length-sorted sequences in snake order
         wl = dict(full, P=len(idx), lens=full["lens"][idx], x=np.ascontiguousarray(full["x"][:, idx]),
@@ -214,7 +336,7 @@ def main():
         T = int(wl["lens"].max())
         wl["x"], wl["tg"] = wl["x"][:T], wl["tg"][:T]
     else:
-        wl = workloads.build(cfg, rank=rank, scale_frames=args.frames_scale)
+        wl = workloads.build(cfg, rank=0 if strong else rank, scale_frames=args.frames_scale)
     layers, P, lens = wl["layers"], wl["P"], wl["lens"]
     T = int(lens.max())
     real_frames = int(lens.sum())
@@ -304,6 +426,10 @@ def main():
         t = torch.tensor([real_frames], device="cuda", dtype=torch.float64)
         dist.all_reduce(t)
         frames_all = int(t.item())
+    rec_paths = net.recurrence_paths()
+    check = None
+    if world > 1 and not args.no_check:
+        check = dp_correctness_record(net, wl, full if strong else None, rank, world, dist, torch, args)
     value = frames_all * args.steps / (ms * 1e-3)
     e2e = frames_all * args.steps / (ms_e2e * 1e-3)
 
@@ -335,35 +461,43 @@ def main():
             roof = {"bound": "hbm", "kernel": top, "achieved": amt / per_launch / 1e9, "peak": pk["hbm"], "unit": "GB/s",
                     "peak_note": "%s copy bandwidth" % pk["src"]}
         roof["frac"] = roof["achieved"] / roof["peak"]
-        # DRAM bytes per launch of the dominant kernel, from the ncu capture summarised in
-        # profiles/lstm_persistent_kernels_cfg1_quarter_frames.md (bytes per unit and frame slot,
-        # scaled by the units x frame slots of one launch; traffic grows in proportion to the frames)
-        per_cell = {"lstm_fwd_recurrence": 26.1, "lstm_bwd_recurrence": 32.2}.get(top)
+        # DRAM bytes (ncu dram__bytes_read.sum + dram__bytes_write.sum) per cell-step of the dominant kernel,
+        # per workload and recurrence path, from captures on reduced frame counts; traffic grows in proportion
+        # to the frame slots, so it is scaled by units x frame slots of one sweep of one layer.  None where no
+        # capture of that kernel on that workload exists.
+        path_fwd = sorted(set(v[0] for v in rec_paths.values()))
+        path_bwd = sorted(set(v[1] for v in rec_paths.values()))
+        per_cell = TRAFFIC_BYTES_PER_CELL_STEP.get((args.workload, top, (path_fwd if "fwd" in top else path_bwd)[0]
+                                                    if (path_fwd and path_bwd) else ""))
         lstm_sizes = [l["size"] for l in layers if l["type"] in ("lstm", "blstm")]
-        if per_cell and lstm_sizes and args.workload == "cfg1" and args.recurrence == 1 and not args.ffma:
+        if per_cell and lstm_sizes and not args.ffma:
             roof["traffic"] = per_cell * (sum(lstm_sizes) / len(lstm_sizes)) * T * P
-            roof["traffic_note"] = "bytes per sweep of one layer (its two side-by-side launches), ncu dram__bytes scaled from a quarter-size capture"
+            roof["traffic_note"] = "bytes per sweep of one layer, ncu dram__bytes of a reduced-frames capture scaled by frame slots"
             roof["launches"] = len(lstm_sizes)
         else:
             roof["traffic"] = None
         roof["share_of_step"] = kernels[top]["share"]
         in_b = int(x_host.numel() * 4 + t_host.numel() * 4 + T * P)
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong" if args.strong else "weak",
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": scaling_of(args, world),
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": c["name"], "parallel_sequences_per_gpu": P, "max_frames": T,
                            "real_frames_per_gpu_step": real_frames, "parallelism": "dp%d" % world,
-                           "recurrence": "persistent" if args.recurrence else "stepwise",
+                           "recurrence_mode_requested": args.recurrence,
+                           "recurrence_forward": "+".join(path_fwd), "recurrence_backward": "+".join(path_bwd),
+                           "sequences_total": c["P"] if strong else P * world,
                            "gemm": "ffma" if args.ffma else "tcgen05_3xtf32",
                            "frames_scale": args.frames_scale,
                            "l2": "working set per step (GBs of state buffers) exceeds the 126 MB L2; no flush needed"},
                 "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": in_b,
                         "d2h_bytes_per_step": 8},
                 "gpu_launches": launches, "roofline": roof, "kernels": kernels, "clocks": sampler.summary()}
+        if check is not None:
+            line["dp_check"] = check
         if world == 1 and not args.no_cpu_baseline:
             try:
                 out = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--workload", args.workload,
-                                      "--steps", "2", "--warmup", "1", "--cpu-seconds", str(args.cpu_seconds)],
+                                      "--steps", "3", "--warmup", "1"],
                                      capture_output=True, text=True, timeout=600)
                 ref_line = [l for l in out.stdout.splitlines() if l.startswith("{")][-1]
                 line["cpu_baseline"] = json.loads(ref_line)["cpu_baseline"]

@@ -64,9 +64,12 @@ int b2_matrix_multiply(float *C, int ldc, const float *A, int lda, int transA, c
  * synchronisation).  No counterpart in the reference toolkit.  Always the FFMA kernel; its split-K
  * partial sums live in a fixed 16 MiB array inside the library image (held by every GPU that loads
  * the library, until exit) instead of an allocation, so the call allocates nothing.
- * Limit: m*n <= 2^21 output elements, otherwise B2_ERR_BAD_SHAPE.
+ * Limit: m*n <= 2^21 output elements, otherwise B2_ERR_BAD_SHAPE; negative sizes or leading
+ * dimensions shorter than a column are B2_ERR_BAD_ARG.
  * The first call on a device looks up the array's device address; make it outside any stream
- * capture.  All calls on a device share the array: calls whose kernels can overlap on the GPU
+ * capture, and before the host program claims the rest of the GPU's memory (the driver backs the
+ * array when the library's code is first used on a device).  A device reset invalidates the address
+ * the library has cached.  All calls on a device share the array: calls whose kernels can overlap on the GPU
  * (different streams) race on it and must be serialised by the caller. */
 int b2_matrix_multiply_noalloc(float *C, int ldc, const float *A, int lda, int transA, const float *B, int ldb,
                                int transB, int m, int n, int k, int accumulate, b2_stream stream);
@@ -119,6 +122,11 @@ int b2_lstm_backward(b2_lstm *layer, const float *weights_dev, const float *x_de
  *      the shape allows it;
  *   4  persistent kernels, every exchange through L2. */
 int b2_lstm_set_recurrence_mode(b2_lstm *layer, int mode);
+/* Which recurrence kernels the layer's last forward (backward = 0) or backward (backward != 0) sweep really
+ * ran, whatever the mode asked for: 0 one launch per timestep, 1 persistent FFMA kernels, 3 tensor-core GEMM
+ * and gate kernel per timestep, 5 persistent tensor-core kernels; -1 before the first sweep.  The reference
+ * has one code path (layers/LstmLayer.cu:1805-1858), so it has no such query. */
+int b2_lstm_recurrence_path(const b2_lstm *layer, int backward);
 /* Waits for the work enqueued on `stream` and reports what the layer's kernels recorded:
  * B2_ERR_STEP_TIMEOUT if a persistent kernel gave up a bounded wait, else B2_OK. */
 int b2_lstm_synchronize(b2_lstm *layer, b2_stream stream);
@@ -140,6 +148,9 @@ typedef struct b2_net b2_net;
 int b2_net_create(const char *network_json, int parallel_sequences, int max_seq_length, unsigned random_seed,
                   b2_net **out);
 void b2_net_destroy(b2_net *net);
+/* Layer::parallelSequences() / Layer::maxSeqLength() (layers/Layer.hpp:163-175) the net was created with */
+int b2_net_parallel_sequences(const b2_net *net);
+int b2_net_max_seq_length(const b2_net *net);
 int b2_net_num_layers(const b2_net *net);
 int b2_net_layer_size(const b2_net *net, int layer);
 /* 0 for layers without weights */
@@ -222,6 +233,8 @@ b2_stream b2_net_stream(b2_net *net);
  * 1 persistent with the exchange the library chooses (default), 2 clusters, 3 tensor-core
  * recurrence, 4 L2 only. */
 int b2_net_set_recurrence_mode(b2_net *net, int mode);
+/* b2_lstm_recurrence_path of layer `layer` of the net; -1 for layers that are no (b)lstm. */
+int b2_net_recurrence_path(b2_net *net, int layer, int backward);
 /* Non-zero forces the FFMA GEMM everywhere (the tensor-core GEMM is the default). */
 int b2_net_set_force_ffma(b2_net *net, int on);
 /* Number of kernels this library has launched on behalf of `net` since creation. */
@@ -238,6 +251,10 @@ int b2_net_get_profile(b2_net *net, int cap, const char **names, float *ms, int 
  * the recorded code, *gave_up = 1 when the block left through the timeout path.  No counterpart in
  * the reference (its kernels have no waits). */
 int b2_selftest_bounded_wait(int *status_out, int *gave_up);
+/* Self-test of how such a failure travels: writes `code` from the HOST into the device status word that the
+ * net's kernels record a given-up wait in, exactly where a kernel would have put it (no kernel is made to fail).
+ * The next b2_net_synchronize, b2_net_train_epoch or b2_optimizer_train must return `code`. */
+int b2_selftest_inject_status(b2_net *net, int code);
 
 /* ------------------------------------------------------------------------------------------
  * Data-parallel training: sequences of a fraction are dealt to the ranks, every rank holds a
@@ -319,7 +336,10 @@ void b2_data_reseed(unsigned seed);
  * (hybrid_online_batch; optimizers/Optimizer.cu:68-231): the next fraction is copied to the device
  * while the current one trains.  *error = sum over fractions of (fraction error / totalSequences)
  * as the reference accumulates it; with learning_rate < 0 nothing is updated (validation pass:
- * forward and error only). */
+ * forward and error only).  The data set must have been opened with the net's parallel_sequences and hold
+ * no sequence longer than the net's max_seq_length (B2_ERR_BAD_SHAPE otherwise).  Before it returns the call
+ * waits for the device once and reports B2_ERR_STEP_TIMEOUT if a kernel gave up a bounded wait during the
+ * epoch (the weights are then not to be trusted). */
 int b2_net_train_epoch(b2_net *net, b2_data *data, float learning_rate, float momentum, double *error,
                        long long *frames);
 /* The same pass as batch learning (no --hybrid_online_batch): gradients of all fractions are summed,

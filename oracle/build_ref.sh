@@ -11,7 +11,8 @@
 # stand-ins in oracle/ref_build/.  Does nothing (exit 0) if the reference checkout is absent.
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
-REF="${REF:-/root/reference}"
+# the reference checkout: $REF, else a directory named "reference" beside this repository
+REF="${REF:-$(cd "$HERE/../.." && pwd)/reference}"
 SRC="$REF/CURRENNT_codes/currennt_lib/src"
 OUT="$HERE/_ref"
 if [ ! -d "$SRC" ]; then echo "build_ref: no reference checkout at $REF, skipping"; exit 0; fi

@@ -41,9 +41,13 @@ SIGNATURES = {
     "b2_lstm_backward": (C.c_int, [C.c_void_p] * 8),
     "b2_lstm_set_recurrence_mode": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_lstm_state_bytes": (C.c_size_t, [C.c_void_p]),
+    "b2_lstm_recurrence_path": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2_net_recurrence_path": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
     "b2_lstm_synchronize": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b2_net_create": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_uint, C.POINTER(C.c_void_p)]),
     "b2_net_destroy": (None, [C.c_void_p]),
+    "b2_net_parallel_sequences": (C.c_int, [C.c_void_p]),
+    "b2_net_max_seq_length": (C.c_int, [C.c_void_p]),
     "b2_net_num_layers": (C.c_int, [C.c_void_p]),
     "b2_net_layer_size": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_net_num_weights": (C.c_size_t, [C.c_void_p, C.c_int]),
@@ -82,6 +86,7 @@ SIGNATURES = {
     "b2_net_set_profiling": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_net_get_profile": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_char_p), _fp, _ip]),
     "b2_selftest_bounded_wait": (C.c_int, [_ip, _ip]),
+    "b2_selftest_inject_status": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_dp_get_unique_id": (C.c_int, [C.c_void_p]),
     "b2_dp_attach": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "b2_dp_detach": (C.c_int, [C.c_void_p]),
@@ -199,6 +204,9 @@ class LstmLayer:
 
     def synchronize(self, stream=None):
         _check(lib().b2_lstm_synchronize(self.h, stream))
+
+    def recurrence_path(self, backward=False):
+        return int(lib().b2_lstm_recurrence_path(self.h, int(backward)))
 
     @property
     def state_bytes(self):
@@ -350,6 +358,22 @@ class Net:
 
     def set_force_ffma(self, on):
         _check(lib().b2_net_set_force_ffma(self.h, int(on)))
+
+    RECURRENCE_PATHS = {0: "stepwise", 1: "persistent_ffma", 3: "tensor_core_per_step", 5: "persistent_tensor_core"}
+
+    def recurrence_path(self, layer, backward=False):
+        """which recurrence kernels layer `layer` really ran in its last sweep (-1: not a (b)lstm layer / none yet)"""
+        return int(lib().b2_net_recurrence_path(self.h, layer, int(backward)))
+
+    def recurrence_paths(self):
+        """{layer index: (forward path name, backward path name)} of the (b)lstm layers"""
+        out = {}
+        for i in range(int(lib().b2_net_num_layers(self.h))):
+            f = self.recurrence_path(i, False)
+            if f >= 0:
+                b = self.recurrence_path(i, True)
+                out[i] = (self.RECURRENCE_PATHS.get(f, str(f)), self.RECURRENCE_PATHS.get(b, str(b)))
+        return out
 
     @property
     def launch_count(self):

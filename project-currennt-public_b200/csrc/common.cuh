@@ -27,6 +27,13 @@ int cuda_fail(cudaError_t e, const char *what, const char *file, int line);
 extern unsigned long long g_launches;
 inline void count_launch(int n = 1) { g_launches += (unsigned long long)n; }
 
+// ---- per-device facts (device.cu) ---------------------------------------------------------------
+constexpr int MAX_DEVICES = 64;
+int current_device();   // ordinal of the current device, -1 when there is none
+int sm_count();         // multiprocessors of the current device
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize), once per kernel and device (the attribute is per context)
+int set_max_dynamic_smem(const void *func, int bytes);
+
 // ---- activation functions ---------------------------------------------------------------------
 // Same formulas and cut-offs as activation_functions/{Logistic,Tanh,Maxmin1}.cuh of the
 // reference: logistic saturates exactly at |x| >= 88.722839, tanh(x) = 2*logistic(2x) - 1.

@@ -21,6 +21,26 @@ struct b2_data {
     const b2::FractionView *last = nullptr;
 };
 
+// The reference takes parallel_sequences and the longest sequence of both the data set and the network from
+// ONE Configuration, so they cannot disagree there; two handles can.  A fraction is laid out [T][P_data][size]:
+// a net with another P would read it mis-strided (and, with a larger P, past the end of the pinned block).
+static int check_data_matches_net(const char *who, b2_net *net, b2_data *data) {
+    if (data->ds.inputPatternSize() != b2_net_layer_size(net, 0) ||
+        data->ds.outputPatternSize() != b2_net_layer_size(net, b2_net_num_layers(net) - 1)) {
+        b2::set_error("%s: the data set has %d inputs / %d targets, the network %d / %d", who,
+                      data->ds.inputPatternSize(), data->ds.outputPatternSize(), b2_net_layer_size(net, 0),
+                      b2_net_layer_size(net, b2_net_num_layers(net) - 1));
+        return B2_ERR_BAD_SHAPE;
+    }
+    if (data->ds.parallelSequences() != b2_net_parallel_sequences(net) || data->ds.maxSeqLength() > b2_net_max_seq_length(net)) {
+        b2::set_error("%s: the data set was opened with parallel_sequences %d and holds sequences of up to %d frames, "
+                      "the network was created for parallel_sequences %d and %d frames", who, data->ds.parallelSequences(),
+                      data->ds.maxSeqLength(), b2_net_parallel_sequences(net), b2_net_max_seq_length(net));
+        return B2_ERR_BAD_SHAPE;
+    }
+    return B2_OK;
+}
+
 extern "C" {
 
 int b2_data_open(b2_data **out, const char *const *nc_paths, int n_files, const b2_data_options *opt) {
@@ -113,13 +133,7 @@ void b2_data_reseed(unsigned seed) { b2::reseed_shuffle_generator(seed); }
 
 int b2_net_train_epoch(b2_net *net, b2_data *data, float learning_rate, float momentum, double *error, long long *frames) {
     if (!net || !data) { b2::set_error("b2_net_train_epoch: null handle"); return B2_ERR_BAD_ARG; }
-    if (data->ds.inputPatternSize() != b2_net_layer_size(net, 0) ||
-        data->ds.outputPatternSize() != b2_net_layer_size(net, b2_net_num_layers(net) - 1)) {
-        b2::set_error("b2_net_train_epoch: the data set has %d inputs / %d targets, the network %d / %d",
-                      data->ds.inputPatternSize(), data->ds.outputPatternSize(), b2_net_layer_size(net, 0),
-                      b2_net_layer_size(net, b2_net_num_layers(net) - 1));
-        return B2_ERR_BAD_SHAPE;
-    }
+    B2_TRY(check_data_matches_net("b2_net_train_epoch", net, data));
     const double nSeqTotal = (double)data->ds.totalSequences();
     double errSum = 0.0;
     long long nFrames = 0;
@@ -156,6 +170,9 @@ int b2_net_train_epoch(b2_net *net, b2_data *data, float learning_rate, float mo
         cur = nxt;
         rc = rcNext;
     }
+    // one read of every layer's status word per epoch: a sweep that gave up a bounded wait returned zeros, and
+    // the caller (b2_optimizer_train) must not store weights trained on them
+    B2_TRY(b2_net_synchronize(net));
     // data-parallel: the epoch's error and frame count are those of all shards
     if (b2_dp_world_size(net) > 1) {
         double fr = (double)nFrames;
@@ -172,6 +189,7 @@ int b2_net_train_epoch(b2_net *net, b2_data *data, float learning_rate, float mo
 // fraction, one update at the end
 int b2_net_train_epoch_batch(b2_net *net, b2_data *data, float learning_rate, float momentum, double *error, long long *frames) {
     if (!net || !data) { b2::set_error("b2_net_train_epoch_batch: null handle"); return B2_ERR_BAD_ARG; }
+    B2_TRY(check_data_matches_net("b2_net_train_epoch_batch", net, data));
     const double nSeqTotal = (double)data->ds.totalSequences();
     double errSum = 0.0;
     long long nFrames = 0;

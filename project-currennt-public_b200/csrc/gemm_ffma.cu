@@ -8,6 +8,8 @@
 // 128x128x16 tiles, 256 threads, 8x8 accumulators per thread, register prefetch of the next
 // k-slab.  Optional split-K over gridDim.z into scratch followed by a fixed-order reduction, so
 // the result does not depend on scheduling.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace b2 {
@@ -136,8 +138,9 @@ int gemm_ffma(float *C, long ldc, const float *A, long sam, long sak, const floa
     // split K when the output tiles alone cannot fill the GPU and K is long
     int tiles = grid.x * grid.y;
     int splits = 1;
-    if (ws && tiles < 148 && k >= 2048) {
-        splits = (2 * 148 + tiles - 1) / tiles;
+    const int sms = sm_count();
+    if (ws && tiles < sms && k >= 2048) {
+        splits = (2 * sms + tiles - 1) / tiles;
         int maxs = k / 512;
         if (splits > maxs) splits = maxs;
         size_t per = (size_t)m * n;
@@ -162,7 +165,7 @@ int gemm_ffma(float *C, long ldc, const float *A, long sam, long sak, const floa
     if (splits > 1) {
         size_t total = (size_t)m * n;
         int blocks = (int)((total + 255) / 256);
-        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (blocks > sms * 8) blocks = sms * 8;
         splitk_reduce_kernel<<<blocks, 256, 0, st>>>(C, ldc, ws, m, n, splits, accumulate ? 1 : 0);
         count_launch();
         B2_CUDA(cudaGetLastError());
@@ -187,12 +190,16 @@ int gemm_ffma(float *C, long ldc, const float *A, long sam, long sak, const floa
 // All calls on a device share the array and find the previous call's partial sums in it: nothing in
 // it has to start at zero, because a launch writes every partial it later reads, but two calls whose
 // kernels overlap on the GPU (different streams) race on it -- serialise them.
+// With lazy module loading the driver gives the array its memory when this module is first used on a device:
+// make the first call before the host program claims the rest of HBM, or that call fails with an out-of-memory
+// error.  The cached address belongs to the device's primary context: after cudaDeviceReset (or the loss of
+// that context) it is stale, and the library must be reloaded.
 namespace {
 constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)1 << 22;
 constexpr size_t NOALLOC_MAX_MN = (size_t)1 << 21;   // largest m*n accepted: leaves room for a 2-way split
 constexpr int NOALLOC_MAX_DEVICES = 64;
 static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
-float *g_noalloc_ptr[NOALLOC_MAX_DEVICES];           // device address of the array, per device ordinal
+std::atomic<float *> g_noalloc_ptr[NOALLOC_MAX_DEVICES];   // device address of the array, per device ordinal
 }  // namespace
 
 extern "C" int b2_matrix_multiply_noalloc(float *C, int ldc, const float *A, int lda, int transA, const float *B, int ldb,
@@ -203,7 +210,18 @@ extern "C" int b2_matrix_multiply_noalloc(float *C, int ldc, const float *A, int
         set_error("b2_matrix_multiply_noalloc: transposing both operands is not supported");
         return B2_ERR_BAD_ARG;
     }
-    if (m < 0 || n < 0 || k < 0 || (size_t)m * (size_t)n > NOALLOC_MAX_MN) {
+    if (m < 0 || n < 0 || k < 0) {
+        set_error("b2_matrix_multiply_noalloc: negative dimension (m %d, n %d, k %d)", m, n, k);
+        return B2_ERR_BAD_ARG;
+    }
+    // leading dimensions must span a column of what they address: C is m x n; A is m x k (k x m when transposed)
+    // and B is k x n (n x k when transposed), all column-major
+    if (ldc < m || lda < (transA ? k : m) || ldb < (transB ? n : k)) {
+        set_error("b2_matrix_multiply_noalloc: leading dimension too small (ldc %d, lda %d, ldb %d for m %d, n %d, k %d)",
+                  ldc, lda, ldb, m, n, k);
+        return B2_ERR_BAD_ARG;
+    }
+    if ((size_t)m * (size_t)n > NOALLOC_MAX_MN) {
         set_error("b2_matrix_multiply_noalloc: m*n = %zu exceeds the fixed scratch limit of %zu output elements",
                   (size_t)m * (size_t)n, NOALLOC_MAX_MN);
         return B2_ERR_BAD_SHAPE;
@@ -214,13 +232,14 @@ extern "C" int b2_matrix_multiply_noalloc(float *C, int ldc, const float *A, int
         set_error("b2_matrix_multiply_noalloc: device ordinal %d outside 0..%d", dev, NOALLOC_MAX_DEVICES - 1);
         return B2_ERR_BAD_ARG;
     }
-    if (!g_noalloc_ptr[dev]) {
-        float *p = nullptr;
-        B2_CUDA(cudaGetSymbolAddress((void **)&p, g_noalloc_scratch));
-        g_noalloc_ptr[dev] = p;
+    float *scratch = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+    if (!scratch) {
+        // threads that race here all look up the same address; the last store wins, with the same value
+        B2_CUDA(cudaGetSymbolAddress((void **)&scratch, g_noalloc_scratch));
+        g_noalloc_ptr[dev].store(scratch, std::memory_order_release);
     }
     const long sam = transA ? lda : 1, sak = transA ? 1 : lda;
     const long sbk = transB ? ldb : 1, sbn = transB ? 1 : ldb;
-    return gemm_ffma(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, accumulate != 0, g_noalloc_ptr[dev], NOALLOC_SCRATCH_FLOATS,
+    return gemm_ffma(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, accumulate != 0, scratch, NOALLOC_SCRATCH_FLOATS,
                      (cudaStream_t)stream);
 }

@@ -487,25 +487,15 @@ int make_map(CUtensorMap *map, const float *base, long inner, long outer, long l
     return B2_OK;
 }
 
-bool g_attr_set = false;
-int g_sm_count = 0;
-
 // one block per SM (the kernel loops over its share of the tiles), fewer when there is less work
-int set_kernel_attributes();
 int persistent_grid(int items) {
-    if (!g_sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sm_count < 1) g_sm_count = 148;
-    }
-    return items < g_sm_count ? items : g_sm_count;
+    const int sms = sm_count();
+    return items < sms ? items : sms;
 }
 
 int set_kernel_attributes() {
-    if (g_attr_set) return B2_OK;
-    B2_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    B2_CUDA(cudaFuncSetAttribute(gemm_tf32x3_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    g_attr_set = true;
+    B2_TRY(set_max_dynamic_smem((const void *)gemm_tf32x3_kernel<64>, SMEM_BYTES));
+    B2_TRY(set_max_dynamic_smem((const void *)gemm_tf32x3_kernel<128>, SMEM_BYTES));
     return B2_OK;
 }
 
@@ -518,7 +508,7 @@ int split_tf32(const float *src, long s_outer, int outer, int inner, float *hi, 
         ((uintptr_t)lo % 16) == 0) {
         const size_t groups = total / 4;
         size_t blocks = (groups + 511) / 512;
-        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (blocks > (size_t)sm_count() * 8) blocks = (size_t)sm_count() * 8;
         if (blocks < 1) blocks = 1;
         split_tf32_vec4_kernel<<<(int)blocks, 256, 0, st>>>(src, s_outer, outer, inner / 4, (float4 *)hi, (float4 *)lo);
         count_launch();
@@ -526,7 +516,7 @@ int split_tf32(const float *src, long s_outer, int outer, int inner, float *hi, 
         return B2_OK;
     }
     size_t blocks = (total + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
     split_tf32_kernel<<<(int)blocks, 256, 0, st>>>(src, s_outer, outer, inner, hi, lo, ldp);
     count_launch();
     B2_CUDA(cudaGetLastError());
@@ -565,7 +555,7 @@ int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, in
     }
     dim3 grid((m + BM - 1) / BM, (n + BN - 1) / BN, 1);
     const int tiles = grid.x * grid.y;
-    // Split K to fill the 148 SMs when there are few output tiles; the partial sums are added with
+    // Split K to fill the SMs when there are few output tiles; the partial sums are added with
     // fp32 FADD in a fixed order.
     int splits = 1;
     if (ws && k >= 1024) {
@@ -606,7 +596,7 @@ int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, in
     if (splits > 1) {
         size_t total = (size_t)m * n;
         int blocks = (int)((total + 255) / 256);
-        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (blocks > sm_count() * 8) blocks = sm_count() * 8;
         tc_splitk_reduce_kernel<<<blocks, 256, 0, st>>>(C, ldc, ws, m, n, splits, accumulate ? 1 : 0);
         count_launch();
         B2_CUDA(cudaGetLastError());
@@ -666,7 +656,7 @@ int tc_batched_reduce(float *C, const long long *c_off, int nbatch, long ldc, co
     for (int b = 0; b < nbatch; ++b) off.c_off[b] = c_off[b];
     const size_t total = (size_t)m * n * nbatch;
     int blocks = (int)((total + 255) / 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     tc_batched_reduce_kernel<<<blocks, 256, 0, st>>>(C, off, ldc, ws, m, n, splits, nbatch);
     count_launch();
     B2_CUDA(cudaGetLastError());

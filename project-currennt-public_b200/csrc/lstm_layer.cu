@@ -110,10 +110,12 @@ int LstmLayerImpl::forward(const float *w, const float *x, float *y, cudaStream_
         if (tcrec_used) {
             B2_TRY(ensure_tcrec());
             rc = lstm_forward_tc(s, bufs, tcrec, w, y, status_dev, st);
+            fwd_path = 3;
         } else if (recurrence_mode >= 1) {
             rc = lstm_persistent(false, persistent_transport(), s, bufs, w, y, nullptr, xchg, status_dev, &tag_next, st);
+            fwd_path = 1;
         }
-        if (rc == 1) rc = lstm_forward_stepwise(s, bufs, w, y, st);
+        if (rc == 1) { rc = lstm_forward_stepwise(s, bufs, w, y, st); fwd_path = 0; }
         B2_TRY(rc);
     }
     forward_done = true;
@@ -130,10 +132,12 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
     {
         Phase ph(*this, "lstm_bwd_recurrence");
         int rc = 1;
-        if (tcrec_used) rc = lstm_backward_tc(s, bufs, tcrec, w, dy, status_dev, st);
-        else if (recurrence_mode >= 1)
+        if (tcrec_used) { rc = lstm_backward_tc(s, bufs, tcrec, w, dy, status_dev, st); bwd_path = 3; }
+        else if (recurrence_mode >= 1) {
             rc = lstm_persistent(true, persistent_transport(), s, bufs, w, nullptr, dy, xchg, status_dev, &tag_next, st);
-        if (rc == 1) rc = lstm_backward_stepwise(s, bufs, w, dy, st);
+            bwd_path = 1;
+        }
+        if (rc == 1) { rc = lstm_backward_stepwise(s, bufs, w, dy, st); bwd_path = 0; }
         B2_TRY(rc);
     }
     const int K = N - P;
@@ -257,7 +261,7 @@ bool LstmLayerImpl::want_tc_recurrence() const {
     if (ps == 0) return s.els >= 256;
     int JB = 0;
     persistent_geometry(s.els, &JB);
-    int slots = 148 / (s.els / JB);
+    int slots = sm_count() / (s.els / JB);
     if (slots < 1) slots = 1;
     const int items = s.D * ((s.P + ps - 1) / ps);
     const int passes = (items + slots - 1) / slots;
@@ -354,6 +358,11 @@ int b2_lstm_set_recurrence_mode(b2_lstm *l, int mode) {
 }
 
 size_t b2_lstm_state_bytes(const b2_lstm *l) { return l ? l->impl.state_bytes : 0; }
+
+int b2_lstm_recurrence_path(const b2_lstm *l, int backward) {
+    if (!l) return -1;
+    return backward ? l->impl.bwd_path : l->impl.fwd_path;
+}
 
 int b2_lstm_synchronize(b2_lstm *l, b2_stream st) {
     if (!l) return B2_ERR_BAD_ARG;

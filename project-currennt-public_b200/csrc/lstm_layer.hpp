@@ -27,6 +27,9 @@ struct LstmLayerImpl {
     // recurrence mode 1 lets the library choose the exchange, 2 forces clusters, 4 forces L2
     int persistent_transport() const { return recurrence_mode == 2 ? 1 : (recurrence_mode == 4 ? 0 : 2); }
     bool tcrec_used = false;      // this fraction's forward sweep ran on the tensor-core recurrence
+    // which recurrence the last forward / backward sweep actually ran: 0 one launch per timestep, 1 persistent
+    // FFMA kernels, 3 tensor-core GEMM + gate kernel per timestep, 5 persistent tensor-core kernels
+    int fwd_path = -1, bwd_path = -1;
     bool want_tc_recurrence() const;
     int ensure_tcrec();
     int check_status(cudaStream_t st);   // synchronises st; returns the kernels' status word

@@ -788,27 +788,14 @@ __global__ void __launch_bounds__(NT, 1) lstm_bwd_persistent_kernel(PersistArgs 
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-int g_num_sms = 0;
-int num_sms() {
-    if (!g_num_sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    }
-    return g_num_sms;
-}
+int num_sms() { return sm_count(); }
 
 template <int ELS, int JB, int PS, bool CL>
 int prepare_kernel(bool backward, void (**kern)(PersistArgs), size_t *smem) {
     typedef Geo<ELS, JB, PS> Gm;
     *kern = backward ? lstm_bwd_persistent_kernel<ELS, JB, PS, CL> : lstm_fwd_persistent_kernel<ELS, JB, PS, CL>;
     *smem = backward ? Gm::bwd_smem(CL) : Gm::fwd_smem(CL);
-    static bool done[2] = {false, false};   // one flag per instantiation and direction
-    if (!done[backward ? 1 : 0]) {
-        B2_CUDA(cudaFuncSetAttribute(*kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)*smem));
-        done[backward ? 1 : 0] = true;
-    }
-    return B2_OK;
+    return set_max_dynamic_smem((const void *)*kern, (int)*smem);
 }
 
 inline void cluster_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, int G, int blocks, size_t smem, cudaStream_t st) {
@@ -905,9 +892,11 @@ bool persistent_geometry(int els, int *JB) {
 
 // 0 when groups of this size do not run as clusters
 int persistent_cluster_slots(int els) {
-    static int s256 = -1, s128 = -1;
-    if (els == 256) { if (s256 < 0) s256 = query_cluster_slots<256, 32>(); return s256; }
-    if (els == 128) { if (s128 < 0) s128 = query_cluster_slots<128, 64>(); return s128; }
+    static int s256[MAX_DEVICES], s128[MAX_DEVICES];   // per device ordinal; 0 = not asked yet, else slots + 1
+    const int dev = current_device();
+    if (dev < 0) return 0;
+    if (els == 256) { if (!s256[dev]) s256[dev] = query_cluster_slots<256, 32>() + 1; return s256[dev] - 1; }
+    if (els == 128) { if (!s128[dev]) s128[dev] = query_cluster_slots<128, 64>() + 1; return s128[dev] - 1; }
     return 0;
 }
 
@@ -994,15 +983,21 @@ int run_part(bool backward, bool use_cluster, PersistArgs a, int els, int PS, in
     return rc;
 }
 
-// second stream for the part of a sweep that runs beside the cluster launch; one per host thread, so that
-// handles driven from different threads do not share the fork / join events
-thread_local cudaStream_t g_aux_stream = nullptr;
-thread_local cudaEvent_t g_fork = nullptr, g_join = nullptr;
-int ensure_aux() {
-    if (g_aux_stream) return B2_OK;
-    B2_CUDA(cudaStreamCreateWithFlags(&g_aux_stream, cudaStreamNonBlocking));
-    B2_CUDA(cudaEventCreateWithFlags(&g_fork, cudaEventDisableTiming));
-    B2_CUDA(cudaEventCreateWithFlags(&g_join, cudaEventDisableTiming));
+// second stream for the part of a sweep that runs beside the cluster launch; one per host thread and device,
+// so that handles driven from different threads (or living on different devices) do not share the fork / join
+// events
+struct AuxStream { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; };
+thread_local AuxStream g_aux[MAX_DEVICES];
+int ensure_aux(AuxStream **out) {
+    const int dev = current_device();
+    if (dev < 0) { set_error("no current CUDA device"); return B2_ERR_CUDA; }
+    AuxStream &a = g_aux[dev];
+    if (!a.stream) {
+        B2_CUDA(cudaStreamCreateWithFlags(&a.stream, cudaStreamNonBlocking));
+        B2_CUDA(cudaEventCreateWithFlags(&a.fork, cudaEventDisableTiming));
+        B2_CUDA(cudaEventCreateWithFlags(&a.join, cudaEventDisableTiming));
+    }
+    *out = &a;
     return B2_OK;
 }
 }  // namespace
@@ -1064,15 +1059,16 @@ int lstm_persistent(bool backward, int transport, const LstmShape &s, const Lstm
     const SweepPlan pl = plan_sweep(s.els, s.P, s.D, transport);
     int ips = 1, rc;
     if (pl.kind == PLAN_MIXED) {
-        B2_TRY(ensure_aux());
-        B2_CUDA(cudaEventRecord(g_fork, st));
-        B2_CUDA(cudaStreamWaitEvent(g_aux_stream, g_fork, 0));
+        AuxStream *aux = nullptr;
+        B2_TRY(ensure_aux(&aux));
+        B2_CUDA(cudaEventRecord(aux->fork, st));
+        B2_CUDA(cudaStreamWaitEvent(aux->stream, aux->fork, 0));
         int ips_cl = 1;
         rc = run_part(backward, true, a, s.els, pl.ps_main, 0, pl.split, st, &ips_cl);
         if (rc != B2_OK) return rc;
-        rc = run_part(backward, false, a, s.els, pl.ps_rest, pl.split, s.P, g_aux_stream, &ips);
-        B2_CUDA(cudaEventRecord(g_join, g_aux_stream));
-        B2_CUDA(cudaStreamWaitEvent(st, g_join, 0));
+        rc = run_part(backward, false, a, s.els, pl.ps_rest, pl.split, s.P, aux->stream, &ips);
+        B2_CUDA(cudaEventRecord(aux->join, aux->stream));
+        B2_CUDA(cudaStreamWaitEvent(st, aux->join, 0));
     } else {
         rc = run_part(backward, pl.kind == PLAN_CLUSTER, a, s.els, pl.ps_main, 0, s.P, st, &ips);
     }

@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(128) tc_bwd_gates_kernel(TcStepArgs a) {
 }  // namespace
 
 namespace {
-// K-splits: enough blocks to fill the 148 SMs, each split a whole number of 32-slabs
+// K-splits: enough blocks to fill the SMs (148 on a B200), each split a whole number of 32-slabs
 int pick_splits(int tiles, int k) {
     int best = 1;
     for (int s = 1; s <= 8; s *= 2)

@@ -8,6 +8,8 @@
 #include <string>
 #include <random>
 
+#include <mutex>
+
 #include "network.hpp"
 
 namespace b2 {
@@ -632,16 +634,24 @@ int b2_matrix_multiply(float *C, int ldc, const float *A, int lda, int transA, c
     if (transA && transB) { set_error("b2_matrix_multiply: transposing both operands is not supported"); return B2_ERR_BAD_ARG; }
     long sam = transA ? lda : 1, sak = transA ? 1 : lda;
     long sbk = transB ? ldb : 1, sbn = transB ? 1 : ldb;
-    // stand-alone calls share one operand arena, split-K scratch and status word per process
-    static TcScratch sc;
-    static int *status = nullptr;
-    static float *ws = nullptr;
+    // stand-alone calls share one operand arena, split-K scratch and status word per DEVICE (the memory belongs
+    // to the device that was current when it was allocated), and run one at a time on a device: the arena is
+    // reused by the next call
+    struct Slot { TcScratch sc; int *status = nullptr; float *ws = nullptr; std::mutex mu; };
+    static Slot slots[MAX_DEVICES];
     static const size_t wsFloats = (size_t)8 << 20;
-    if (!status) {
-        B2_CUDA(cudaMalloc(&status, sizeof(int)));
-        B2_CUDA(cudaMemset(status, 0, sizeof(int)));
-        B2_CUDA(cudaMalloc(&ws, wsFloats * sizeof(float)));
+    const int dev = current_device();
+    if (dev < 0) { set_error("b2_matrix_multiply: no current CUDA device"); return B2_ERR_CUDA; }
+    Slot &sl = slots[dev];
+    std::lock_guard<std::mutex> lk(sl.mu);
+    if (!sl.status) {
+        B2_CUDA(cudaMalloc(&sl.status, sizeof(int)));
+        B2_CUDA(cudaMemset(sl.status, 0, sizeof(int)));
+        B2_CUDA(cudaMalloc(&sl.ws, wsFloats * sizeof(float)));
     }
+    TcScratch &sc = sl.sc;
+    int *status = sl.status;
+    float *ws = sl.ws;
     B2_TRY(gemm_auto(C, ldc, A, sam, sak, B, sbk, sbn, m, n, k, accumulate != 0, force_ffma != 0, &sc, ws, wsFloats, status,
                      (cudaStream_t)stream));
     if (!force_ffma && gemm_wants_tc(sam, sak, sbk, sbn, m, n, k)) {
@@ -667,6 +677,14 @@ int b2_net_create(const char *network_json, int P, int maxT, unsigned seed, b2_n
     return B2_OK;
 }
 void b2_net_destroy(b2_net *n) { delete n; }
+int b2_selftest_inject_status(b2_net *n, int code) {
+    if (!n) return B2_ERR_BAD_ARG;
+    B2_CUDA(cudaStreamSynchronize(n->net.stream));
+    B2_CUDA(cudaMemcpy(n->net.statusDev, &code, sizeof(int), cudaMemcpyHostToDevice));
+    return B2_OK;
+}
+int b2_net_parallel_sequences(const b2_net *n) { return n ? n->net.P : 0; }
+int b2_net_max_seq_length(const b2_net *n) { return n ? n->net.maxT : 0; }
 int b2_net_num_layers(const b2_net *n) { return n ? (int)n->net.layers.size() : 0; }
 int b2_net_layer_size(const b2_net *n, int i) {
     return (n && i >= 0 && i < (int)n->net.layers.size()) ? n->net.layers[i]->size() : 0;
@@ -803,6 +821,12 @@ int b2_net_get_outputs(b2_net *n, int i, float *host) { return copy_layer_vec(n,
 int b2_net_get_output_errors(b2_net *n, int i, float *host) { return copy_layer_vec(n, i, host, true); }
 int b2_net_synchronize(b2_net *n) { return n ? n->net.synchronize() : B2_ERR_BAD_ARG; }
 b2_stream b2_net_stream(b2_net *n) { return n ? (b2_stream)n->net.stream : nullptr; }
+int b2_net_recurrence_path(b2_net *n, int layer, int backward) {
+    if (!n || layer < 0 || layer >= (int)n->net.layers.size()) return -1;
+    LstmLayer *l = dynamic_cast<LstmLayer *>(n->net.layers[layer].get());
+    if (!l) return -1;
+    return backward ? l->impl().bwd_path : l->impl().fwd_path;
+}
 int b2_net_set_recurrence_mode(b2_net *n, int mode) { if (!n) return B2_ERR_BAD_ARG; n->net.recurrenceMode = mode; return B2_OK; }
 int b2_net_set_force_ffma(b2_net *n, int on) { if (!n) return B2_ERR_BAD_ARG; n->net.forceFfma = on != 0; return B2_OK; }
 unsigned long long b2_net_launch_count(const b2_net *n) { return n ? g_launches - n->net.launchesAtCreate : 0; }

@@ -109,3 +109,48 @@ def test_first_fraction_of_a_data_set_matches_the_checker(tmp_path):
         got["dw%d" % i] = net.weight_updates(i)
     parity.compare_run(layers, got, want, "nc fraction", lstm_pad_zero_lens=lens)
     net.close()
+
+
+def test_epoch_loop_rejects_a_data_set_opened_for_another_batch_shape(tmp_path):
+    """The reference reads parallel_sequences and the sequence length limit of data set and network from one
+    Configuration; here they are two handles, and a mismatch must be refused, not trained on mis-strided frames."""
+    import b2lstm
+    layers = L(("input", 5), ("lstm", 8), ("feedforward_identity", 2), ("sse", 2))
+    path = corpus(tmp_path, [6, 9, 4, 7], 5, 2, 9)
+    for net_P, net_T, data_P in [(4, 9, 2), (2, 9, 4), (2, 8, 2)]:
+        net = b2lstm.Net(layers, net_P, net_T)
+        ds = b2lstm.DataSet(path, data_P)
+        for fn in (b2lstm.train_epoch, b2lstm.train_epoch_batch):
+            with pytest.raises(b2lstm.B2Error, match="error -1"):       # B2_ERR_BAD_SHAPE
+                fn(net, ds, 1e-3, 0.9)
+        ds.close()
+        net.close()
+
+
+def test_a_recorded_timeout_reaches_the_caller_of_the_epoch_loop(tmp_path):
+    """A kernel that gives up a bounded wait records B2_ERR_STEP_TIMEOUT in a device status word.  Written there
+    from the host (no kernel is made to fail), the code must come back from the epoch loop and from the training
+    run, which must not go on to store the weights; afterwards the net trains normally."""
+    import b2lstm
+    from b2lstm.lib import lib
+    layers = L(("input", 5), ("blstm", 16), ("feedforward_identity", 2), ("sse", 2))
+    path = corpus(tmp_path, [6, 9, 4, 7, 8], 5, 2, 10)
+    net = b2lstm.Net(layers, 2, 9)
+    ds = b2lstm.DataSet(path, 2)
+    assert lib().b2_selftest_inject_status(net.h, -3) == 0
+    with pytest.raises(b2lstm.B2Error, match="error -3"):
+        b2lstm.train_epoch(net, ds, 1e-3, 0.9)
+    ds.close()
+    ds = b2lstm.DataSet(path, 2)
+    opt = b2lstm.Optimizer(net, ds, max_epochs=3)
+    assert lib().b2_selftest_inject_status(net.h, -3) == 0
+    with pytest.raises(b2lstm.B2Error, match="error -3"):
+        opt.train()
+    assert opt.state()["cur_epoch"] == 1
+    opt.close()
+    ds.close()
+    ds = b2lstm.DataSet(path, 2)
+    err, frames = b2lstm.train_epoch(net, ds, 1e-3, 0.9)                 # the status word was cleared by the report
+    assert frames == 34 and err > 0
+    ds.close()
+    net.close()

@@ -18,7 +18,8 @@ VARIANT_IDS = ["stepwise-ffma", "persistent-ffma", "persistent-tensor", "persist
                "stepwise-tensor", "persistent_l2-tensor"]
 
 
-def run_gpu(layers, P, lens, x, tg, weights, variant, lr=1e-4, mom=0.9, maxT=None):
+def run_gpu(layers, P, lens, x, tg, weights, variant, lr=1e-4, mom=0.9, maxT=None, paths=None):
+    """paths: optional dict that receives {layer: (forward path, backward path)} of the (b)lstm layers"""
     import b2lstm
     net = b2lstm.Net(layers, P, maxT or x.shape[0])
     net.set_recurrence_mode(variant["recurrence"])
@@ -40,6 +41,8 @@ def run_gpu(layers, P, lens, x, tg, weights, variant, lr=1e-4, mom=0.9, maxT=Non
             out["dw%d" % i] = net.weight_updates(i)
     net.update_weights(lr, mom)
     net.synchronize()
+    if paths is not None:
+        paths.update(net.recurrence_paths())
     for i in weights:
         out["wnew%d" % i] = net.get_weights(i)
     out["launches"] = net.launch_count
@@ -114,6 +117,40 @@ def test_config_layer_sizes_reduced_frames(cfg, P, scale, variant):
     want = run_kind(checker(), wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"])
     got = run_gpu(wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"], variant)
     parity.compare_run(wl["layers"], got, want, "cfg%d reduced" % cfg, lstm_pad_zero_lens=wl["lens"])
+
+
+def test_cfg2_stack_takes_the_large_batch_recurrence():
+    """Configuration 2's own stack (512 -> 4x blstm 1024/direction -> 256) with 16 parallel sequences on a few
+    frames, recurrence mode 1 (the library chooses): the choice must be a tensor-core recurrence, as for the
+    full-size workload, and the result must match the checker."""
+    from b2lstm import workloads
+    wl = workloads.build(2, scale_frames=0.004, P=16)
+    want = run_kind(checker(), wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"])
+    paths = {}
+    got = run_gpu(wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"], dict(recurrence=1, ffma=0), paths=paths)
+    assert sorted(paths) == [1, 2, 3, 4]
+    for i, (f, b) in paths.items():
+        assert f in ("tensor_core_per_step", "persistent_tensor_core") and b == f, (i, f, b)
+    parity.compare_run(wl["layers"], got, want, "cfg2 stack", lstm_pad_zero_lens=wl["lens"])
+
+
+def test_cfg1_fraction_at_full_size_against_the_reference():
+    """One fraction of configuration 1 at FULL size (32 sequences of 300..1200 frames, about 24k frames): error,
+    every layer's outputs, the output errors into the blstm layers and every gradient block against the
+    reference's own code (its OpenMP host build: same sources and the same per-weight summation order as the
+    serial build, about a minute on the host cores)."""
+    from b2lstm import workloads
+    from oracle import ref_available
+    if not ref_available(omp=True):
+        pytest.skip("the OpenMP build of the reference did not travel with the repository")
+    import os
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+    wl = workloads.build(1)
+    want = run_kind("ref_omp", wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"])
+    paths = {}
+    got = run_gpu(wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"], dict(recurrence=1, ffma=0), paths=paths)
+    print("cfg1 full size: recurrence paths", paths, "error", got["loss"], "reference", want["loss"])
+    parity.compare_run(wl["layers"], got, want, "cfg1 full size", lstm_pad_zero_lens=wl["lens"])
 
 
 @pytest.mark.parametrize("variant", VARIANTS[1:5] + VARIANTS[6:], ids=VARIANT_IDS[1:5] + VARIANT_IDS[6:])

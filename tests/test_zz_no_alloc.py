@@ -46,3 +46,36 @@ def test_noalloc_rejects_sizes_beyond_its_fixed_scratch():
     t = torch.zeros(8, device="cuda:0")
     with pytest.raises(b2lstm.B2Error, match="fixed scratch limit"):
         b2lstm.matrix_multiply_noalloc(t, 4096, t, 4096, 0, t, 8, 0, 4096, 4096, 8)
+
+
+def test_noalloc_rejects_negative_sizes_and_short_leading_dimensions():
+    import torch
+    import b2lstm
+    t = torch.zeros(64, device="cuda:0")
+    for args in [(t, 4, t, 4, 0, t, 4, 0, -1, 4, 4), (t, 3, t, 4, 0, t, 4, 0, 4, 4, 4), (t, 4, t, 3, 0, t, 4, 0, 4, 4, 4),
+                 (t, 4, t, 4, 0, t, 3, 0, 4, 4, 4), (t, 4, t, 3, 1, t, 4, 0, 4, 4, 4)]:
+        with pytest.raises(b2lstm.B2Error, match="error -5"):            # B2_ERR_BAD_ARG
+            b2lstm.matrix_multiply_noalloc(*args)
+
+
+def test_noalloc_leaves_the_free_device_memory_unchanged():
+    """What the name promises, observed from outside: once the first call on the device has been made, further
+    calls (split-K shapes included) leave cudaMemGetInfo's free byte count exactly where it was."""
+    import torch
+    import b2lstm
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(3)
+    shapes = [(96, 80, 6000), (64, 64, 4096), (200, 33, 2500)]
+    ops = []
+    for m, n, k in shapes:                                   # all operands exist before the measurement starts
+        ops.append((torch.from_numpy(rng.standard_normal((k, m)).astype(np.float32)).to(dev),
+                    torch.from_numpy(rng.standard_normal((n, k)).astype(np.float32)).to(dev),
+                    torch.empty((n, m), device=dev), m, n, k))
+    A, B, Cm, m, n, k = ops[0]
+    b2lstm.matrix_multiply_noalloc(Cm, m, A, m, 0, B, k, 0, m, n, k)          # first call: address look-up
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    for A, B, Cm, m, n, k in ops[1:] + ops:
+        b2lstm.matrix_multiply_noalloc(Cm, m, A, m, 0, B, k, 0, m, n, k)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free0
