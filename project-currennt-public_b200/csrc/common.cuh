@@ -169,6 +169,21 @@ int lstm_forward_tc(const LstmShape &s, const LstmBuffers &bf, const TcRecBuffer
 int lstm_backward_tc(const LstmShape &s, const LstmBuffers &bf, const TcRecBuffers &rb, const float *w, const float *dy,
                      int *status, cudaStream_t st);
 
+// persistent tensor-core recurrence (lstm_ptc.cu): recurrent weights resident in shared memory as fp16 hi/lo
+// tcgen05 operands for the whole sweep.  Returns B2_OK, an error, or 1 when the shape is not covered.
+struct PtcBuffers {
+    unsigned *maxbits = nullptr;                   // [2] largest |w| of the recurrent block per direction (float bits)
+    float *scale = nullptr;                        // [direction][2]: S, 1/S
+    uint4 *wimg_f = nullptr, *wimg_b = nullptr;    // per-block weight images of the forward / backward sweep
+    unsigned long long *xh = nullptr, *xe = nullptr;   // exchange words of the forward / backward sweep
+};
+bool lstm_ptc_supported(const LstmShape &s);
+size_t lstm_ptc_image_bytes(int els, int D);
+void lstm_ptc_exchange_words(int els, int P, int D, size_t *xh_words, size_t *xe_words);
+int lstm_ptc_prepare(const LstmShape &s, const float *w, const PtcBuffers &pb, cudaStream_t st);
+int lstm_ptc_sweep(bool backward, const LstmShape &s, const LstmBuffers &b, const PtcBuffers &pb, const float *w, float *y,
+                   const float *dy, int *status, unsigned *tag_next, cudaStream_t st);
+
 // persistent kernels (lstm_persistent.cu).  Return B2_OK, an error, or 1 when the shape has no
 // persistent kernel (the caller then uses the stepwise kernels).
 bool persistent_geometry(int els, int *JB);   // hidden units per block of the register-resident geometry

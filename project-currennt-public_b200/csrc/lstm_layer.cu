@@ -69,6 +69,8 @@ void LstmLayerImpl::destroy() {
     cudaFree(tcrec.wrec_hi); cudaFree(tcrec.wrec_lo); cudaFree(tcrec.y_hi); cudaFree(tcrec.y_lo);
     cudaFree(tcrec.d_hi); cudaFree(tcrec.d_lo); cudaFree(tcrec.part);
     tcrec = TcRecBuffers();
+    cudaFree(ptc.maxbits); cudaFree(ptc.scale); cudaFree(ptc.wimg_f); cudaFree(ptc.wimg_b); cudaFree(ptc.xh); cudaFree(ptc.xe);
+    ptc = PtcBuffers();
     if (own_scratch) { own_scratch->release(); delete own_scratch; own_scratch = nullptr; scratch = nullptr; }
     bufs = LstmBuffers();
     ws = nullptr; xchg = nullptr; status_dev = nullptr;
@@ -106,8 +108,17 @@ int LstmLayerImpl::forward(const float *w, const float *x, float *y, cudaStream_
         Phase ph(*this, "lstm_fwd_recurrence");
         B2_TRY(lstm_prepare_wrecT(s, w, bufs.wrecT, st));
         int rc = 1;
-        tcrec_used = want_tc_recurrence();
-        if (tcrec_used) {
+        ptc_used = want_ptc();
+        if (ptc_used) {
+            B2_TRY(ensure_ptc());
+            B2_TRY(lstm_ptc_prepare(s, w, ptc, st));
+            rc = lstm_ptc_sweep(false, s, bufs, ptc, w, y, nullptr, status_dev, &tag_next, st);
+            fwd_path = 5;
+            if (rc == 1) ptc_used = false;
+        }
+        tcrec_used = !ptc_used && want_tc_recurrence();
+        if (ptc_used) {
+        } else if (tcrec_used) {
             B2_TRY(ensure_tcrec());
             rc = lstm_forward_tc(s, bufs, tcrec, w, y, status_dev, st);
             fwd_path = 3;
@@ -132,7 +143,12 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
     {
         Phase ph(*this, "lstm_bwd_recurrence");
         int rc = 1;
-        if (tcrec_used) { rc = lstm_backward_tc(s, bufs, tcrec, w, dy, status_dev, st); bwd_path = 3; }
+        if (ptc_used && recurrence_mode != 6) {
+            rc = lstm_ptc_sweep(true, s, bufs, ptc, w, nullptr, dy, status_dev, &tag_next, st);
+            bwd_path = 5;
+        }
+        if (rc != 1) {
+        } else if (tcrec_used) { rc = lstm_backward_tc(s, bufs, tcrec, w, dy, status_dev, st); bwd_path = 3; }
         else if (recurrence_mode >= 1) {
             rc = lstm_persistent(true, persistent_transport(), s, bufs, w, nullptr, dy, xchg, status_dev, &tag_next, st);
             bwd_path = 1;
@@ -266,6 +282,30 @@ bool LstmLayerImpl::want_tc_recurrence() const {
     const int items = s.D * ((s.P + ps - 1) / ps);
     const int passes = (items + slots - 1) / slots;
     return passes * (1.4 + 0.27 * ps) > 12.0;
+}
+
+// The persistent tensor-core kernels serve 512 units per direction; modes 5 and 6 select them.
+bool LstmLayerImpl::want_ptc() const {
+    const LstmShape s = shape();
+    if (force_ffma || !lstm_ptc_supported(s)) return false;
+    return recurrence_mode == 5 || recurrence_mode == 6;
+}
+
+int LstmLayerImpl::ensure_ptc() {
+    if (ptc.wimg_f) return B2_OK;
+    const size_t img = lstm_ptc_image_bytes(els, D);
+    size_t xh = 0, xe = 0;
+    lstm_ptc_exchange_words(els, desc.parallel_sequences, D, &xh, &xe);
+    B2_CUDA(cudaMalloc(&ptc.maxbits, 2 * sizeof(unsigned)));
+    B2_CUDA(cudaMalloc(&ptc.scale, 4 * sizeof(float)));
+    B2_CUDA(cudaMalloc(&ptc.wimg_f, img));
+    B2_CUDA(cudaMalloc(&ptc.wimg_b, img));
+    B2_CUDA(cudaMalloc(&ptc.xh, xh * sizeof(unsigned long long)));
+    B2_CUDA(cudaMalloc(&ptc.xe, xe * sizeof(unsigned long long)));
+    B2_CUDA(cudaMemset(ptc.xh, 0, xh * sizeof(unsigned long long)));   // tag 0 is never waited for
+    B2_CUDA(cudaMemset(ptc.xe, 0, xe * sizeof(unsigned long long)));
+    state_bytes += 2 * img + (xh + xe) * sizeof(unsigned long long);
+    return B2_OK;
 }
 
 int LstmLayerImpl::ensure_tcrec() {

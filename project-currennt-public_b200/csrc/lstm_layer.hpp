@@ -24,9 +24,15 @@ struct LstmLayerImpl {
     unsigned tag_next = 1;
     // tensor-core recurrence (large batches): hi/lo buffers, allocated on first use
     TcRecBuffers tcrec{};
-    // recurrence mode 1 lets the library choose the exchange, 2 forces clusters, 4 forces L2
+    // recurrence mode 1 lets the library choose, 2 forces clusters, 4 forces L2, 5 the persistent tensor-core
+    // kernels, 6 those for the forward sweep only
     int persistent_transport() const { return recurrence_mode == 2 ? 1 : (recurrence_mode == 4 ? 0 : 2); }
     bool tcrec_used = false;      // this fraction's forward sweep ran on the tensor-core recurrence
+    // persistent tensor-core recurrence: weight images, exchange words (allocated on first use)
+    PtcBuffers ptc{};
+    bool ptc_used = false;        // this fraction's forward sweep ran on the persistent tensor-core kernels
+    bool want_ptc() const;
+    int ensure_ptc();
     // which recurrence the last forward / backward sweep actually ran: 0 one launch per timestep, 1 persistent
     // FFMA kernels, 3 tensor-core GEMM + gate kernel per timestep, 5 persistent tensor-core kernels
     int fwd_path = -1, bwd_path = -1;

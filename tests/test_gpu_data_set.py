@@ -146,7 +146,7 @@ def test_a_recorded_timeout_reaches_the_caller_of_the_epoch_loop(tmp_path):
     assert lib().b2_selftest_inject_status(net.h, -3) == 0
     with pytest.raises(b2lstm.B2Error, match="error -3"):
         opt.train()
-    assert opt.state()["cur_epoch"] == 1
+    assert opt.state["cur_epoch"] == 1
     opt.close()
     ds.close()
     ds = b2lstm.DataSet(path, 2)

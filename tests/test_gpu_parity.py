@@ -173,6 +173,55 @@ def test_persistent_geometries(ls, bi, P, lens, variant):
     parity.compare_run(layers, got, want, "ls%d bi%d P%d" % (ls, bi, P), lstm_pad_zero_lens=lens)
 
 
+@pytest.mark.parametrize("mode", [6, 5], ids=["forward_only", "forward_and_backward"])
+@pytest.mark.parametrize("ls,bi,P,lens", [(1024, 1, 16, [14] * 10 + [12, 9, 9, 5, 2, 1]),
+                                          (1024, 1, 32, [9] * 30 + [5, 2]),
+                                          (1024, 1, 5, [12, 12, 7, 3, 12]),
+                                          (512, 0, 20, [11] * 12 + [10, 9, 8, 7, 6, 5, 4, 3]),
+                                          (1024, 1, 40, [7] * 20 + [5] * 19 + [2]),
+                                          (1024, 1, 83, [6] * 80 + [3, 2, 1]),
+                                          (1024, 1, 150, [4] * 100 + [3] * 50)])
+def test_persistent_tensor_core_recurrence(ls, bi, P, lens, mode):
+    """The persistent tensor-core kernels (512 units per direction; recurrent weights resident in shared memory
+    as fp16 hi/lo operands): one chunk and several chunks per group of blocks, chunks of 16 and of 32 sequences,
+    sequence counts that do not fill the last chunk, ragged lengths, one and two directions.  Mode 6 runs only
+    the forward sweep on them (the backward sweep on the FFMA kernels), mode 5 both."""
+    from b2lstm import workloads
+    layers = L(("input", 16), ("blstm" if bi else "lstm", ls), ("feedforward_identity", 8), ("sse", 8))
+    lens = np.array(lens, np.int32)
+    x, tg = workloads.make_fraction(16, 8, P, lens, 51, 52)
+    w = workloads.make_weights(layers, 53, 0.08)
+    want = run_kind(checker(), layers, P, lens, x, tg, w)
+    paths = {}
+    got = run_gpu(layers, P, lens, x, tg, w, dict(recurrence=mode, ffma=0), paths=paths)
+    assert paths[1][0] == "persistent_tensor_core", paths
+    assert paths[1][1] == ("persistent_tensor_core" if mode == 5 else "persistent_ffma"), paths
+    parity.compare_run(layers, got, want, "ls%d bi%d P%d" % (ls, bi, P), lstm_pad_zero_lens=lens)
+    again = run_gpu(layers, P, lens, x, tg, w, dict(recurrence=mode, ffma=0))
+    for key in got:
+        if key != "launches":
+            assert np.array_equal(np.asarray(got[key]), np.asarray(again[key])), "not deterministic: " + key
+
+
+def test_persistent_tensor_core_recurrence_with_large_weights_and_activations():
+    """Recurrent weights far from the usual range (one direction scaled by 40, the other by 1/300) and targets
+    that drive the deltas into the clip: the per-direction power-of-two scale of the fp16 operands must keep
+    the result within the same bounds.  Two frames only: with weights this large the recurrence amplifies any
+    rounding difference tenfold per step, so longer sequences compare chaos, not arithmetic."""
+    from b2lstm import workloads
+    layers = L(("input", 16), ("blstm", 1024), ("feedforward_identity", 8), ("sse", 8))
+    P, lens = 16, np.array([2] * 14 + [1, 1], np.int32)
+    x, tg = workloads.make_fraction(16, 8, P, lens, 61, 62, target_scale=300.0)
+    w = workloads.make_weights(layers, 63, 0.02)
+    ls, els, pls = 1024, 512, 16
+    rec = w[1][4 * ls * (pls + 1):4 * ls * (pls + 1) + 4 * ls * els].reshape(4, 2, els, els)
+    rec[:, 0] *= 40.0
+    rec[:, 1] /= 300.0
+    want = run_kind(checker(), layers, P, lens, x, tg, w)
+    got = run_gpu(layers, P, lens, x, tg, w, dict(recurrence=5, ffma=0))
+    parity.compare_run(layers, got, want, "scaled recurrent weights", lstm_pad_zero_lens=lens)
+
+
 @pytest.mark.parametrize("variant", [VARIANTS[2], VARIANTS[5]], ids=[VARIANT_IDS[2], VARIANT_IDS[5]])
 @pytest.mark.parametrize("ls,bi,P,lens", [(320, 1, 8, [40] * 6 + [33, 21]), (200, 0, 6, [50, 50, 47, 30, 22, 9]),
                                           (150, 0, 5, [60, 55, 50, 45, 40]), (384, 1, 4, [70, 64, 31, 70])])
