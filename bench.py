@@ -297,6 +297,9 @@ def main():
     ap.add_argument("--frames-scale", type=float, default=1.0,
                     help="shorten every sequence by this factor (profiler captures only; such a line is not a bench value)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="one GPU only: run rank 0's share of a W-way split of the workload, without the all-reduce (kernel tuning; "
+                         "such a line is not a bench value)")
     ap.add_argument("--gemm", default="", help="m,n,k,ta,tb: time b2_matrix_multiply on one shape instead of the train step")
     args = ap.parse_args()
     if args.gemm:
@@ -327,10 +330,10 @@ def main():
     cfg = int(args.workload.replace("cfg", ""))
     c = workloads.CONFIGS[cfg]
     strong = scaling_of(args, world) == "strong"
-    if strong and world > 1:
+    if (strong and world > 1) or (world == 1 and args.shard_of > 1):
         full = workloads.build(cfg, scale_frames=args.frames_scale)
         from b2lstm import dp
-        idx = dp.shard_indices(c["P"], rank, world)   # deal the length-sorted sequences in snake order
+        idx = dp.shard_indices(c["P"], rank, world if world > 1 else args.shard_of)   # deal the length-sorted sequences in snake order
         wl = dict(full, P=len(idx), lens=full["lens"][idx], x=np.ascontiguousarray(full["x"][:, idx]),
                   tg=np.ascontiguousarray(full["tg"][:, idx]))
         T = int(wl["lens"].max())
@@ -487,7 +490,7 @@ def main():
                            "recurrence_forward": "+".join(path_fwd), "recurrence_backward": "+".join(path_bwd),
                            "sequences_total": c["P"] if strong else P * world,
                            "gemm": "ffma" if args.ffma else "tcgen05_3xtf32",
-                           "frames_scale": args.frames_scale,
+                           "frames_scale": args.frames_scale, "emulated_shard_of": args.shard_of,
                            "l2": "working set per step (GBs of state buffers) exceeds the 126 MB L2; no flush needed"},
                 "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": in_b,
                         "d2h_bytes_per_step": 8},

@@ -120,7 +120,11 @@ int b2_lstm_backward(b2_lstm *layer, const float *weights_dev, const float *x_de
  *      direction), through L2 otherwise;
  *   3  tensor-core recurrence (one batched tcgen05 GEMM and one gate kernel per timestep) wherever
  *      the shape allows it;
- *   4  persistent kernels, every exchange through L2. */
+ *   4  persistent kernels, every exchange through L2;
+ *   5  persistent tensor-core kernels (recurrent weights resident in shared memory as fp16 hi/lo tcgen05 operands for
+ *      the whole sweep) wherever the shape allows it (512 units per direction); mode 1 picks them by itself from 16
+ *      parallel sequences on;
+ *   6  as 5 for the forward sweep only (the backward sweep runs on the mode-1 kernels). */
 int b2_lstm_set_recurrence_mode(b2_lstm *layer, int mode);
 /* Which recurrence kernels the layer's last forward (backward = 0) or backward (backward != 0) sweep really
  * ran, whatever the mode asked for: 0 one launch per timestep, 1 persistent FFMA kernels, 3 tensor-core GEMM
@@ -230,8 +234,8 @@ int b2_net_synchronize(b2_net *net);
 /* The stream all of the net's work is ordered on (a cudaStream_t). */
 b2_stream b2_net_stream(b2_net *net);
 /* The recurrence mode of every (b)lstm layer, values as for b2_lstm_set_recurrence_mode: 0 stepwise,
- * 1 persistent with the exchange the library chooses (default), 2 clusters, 3 tensor-core
- * recurrence, 4 L2 only. */
+ * 1 persistent kernels of the library's choice (default), 2 clusters, 3 tensor-core GEMM per step,
+ * 4 L2 only, 5 persistent tensor-core kernels, 6 those for the forward sweep only. */
 int b2_net_set_recurrence_mode(b2_net *net, int mode);
 /* b2_lstm_recurrence_path of layer `layer` of the net; -1 for layers that are no (b)lstm. */
 int b2_net_recurrence_path(b2_net *net, int layer, int backward);

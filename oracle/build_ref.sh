@@ -16,7 +16,8 @@ REF="${REF:-$(cd "$HERE/../.." && pwd)/reference}"
 SRC="$REF/CURRENNT_codes/currennt_lib/src"
 OUT="$HERE/_ref"
 if [ ! -d "$SRC" ]; then echo "build_ref: no reference checkout at $REF, skipping"; exit 0; fi
-if [ -f "$OUT/libcurrennt_ref.so" ] && [ -f "$OUT/libcurrennt_ref_omp.so" ] && [ -z "$FORCE" ] \
+if [ -f "$OUT/libcurrennt_ref.so" ] && [ -f "$OUT/libcurrennt_ref_omp.so" ] && [ -f "$OUT/libcurrennt_ref_b200.so" ] && [ -z "$FORCE" ] \
+   && [ "$OUT/libcurrennt_ref_b200.so" -nt "$HERE/../project-currennt-public_b200/adapter/LstmLayerB200.hpp" ] \
    && [ "$OUT/libcurrennt_ref.so" -nt "$HERE/ref_build/ref_harness.cu" ] \
    && [ "$OUT/libcurrennt_ref.so" -nt "$HERE/ref_build/cfgstub.cpp" ]; then
   echo "build_ref: up to date"; exit 0
@@ -53,5 +54,15 @@ LINK_EXTRA=()
 build_variant ""
 LINK_EXTRA=(-lgomp)
 build_variant "_omp" -Xcompiler -fopenmp -DTHRUST_HOST_SYSTEM=THRUST_HOST_SYSTEM_OMP
+# The drop-in claim, compiled: the reference's Gpu-device classes (device code for the B200) with the adapter class
+# project-currennt-public_b200/adapter/LstmLayerB200.hpp in place of LstmLayer<Gpu>, linked against libb2lstm.so
+# (found at run time beside this repository's package through the run path).
+PKG="$(cd "$HERE/../project-currennt-public_b200" && pwd)"
+if [ -f "$PKG/libb2lstm.so" ]; then
+  LINK_EXTRA=(-L"$PKG" -lb2lstm -Xlinker -rpath -Xlinker '$ORIGIN/../../project-currennt-public_b200')
+  build_variant "_b200" -gencode arch=compute_100a,code=sm_100a -DREF_WITH_B200_ADAPTER -I"$PKG/adapter" -I"$HERE/../include"
+else
+  echo "build_ref: libb2lstm.so not built yet, skipping the adapter variant"
+fi
 rm -rf "$B"
 ls -la "$OUT"

@@ -3,6 +3,9 @@
 * kind="ref" / "ref_omp": the reference toolkit's own Cpu-device layer classes, compiled from
   the reference sources by oracle/build_ref.sh into oracle/_ref/ (serial / OpenMP Thrust host
   backend).  Available only where that library has been built.
+* kind="ref_b200": the reference toolkit's own Gpu-device layer classes with layers::LstmLayerB200<Gpu> (the
+  adapter class of this repository, compiled against the reference's headers) in place of LstmLayer<Gpu>;
+  needs a GPU and the built library.  It is the compiled form of the drop-in claim, not a checker.
 * kind="port" / "port64": the plain-C restatement in oracle/currennt_oracle.c (fp32 / fp64).
 
 Only tests/, the smoke check and the CPU-baseline leg of the benchmark may import this module.
@@ -28,16 +31,17 @@ def _ptr(a, t=_fp):
     return a.ctypes.data_as(t)
 
 
-def ref_available(omp=False):
-    return os.path.exists(os.path.join(HERE, "_ref", "libcurrennt_ref_omp.so" if omp else "libcurrennt_ref.so"))
+def ref_available(omp=False, adapter=False):
+    name = "libcurrennt_ref_b200.so" if adapter else ("libcurrennt_ref_omp.so" if omp else "libcurrennt_ref.so")
+    return os.path.exists(os.path.join(HERE, "_ref", name))
 
 
 def _load(kind):
-    if kind in ("ref", "ref_omp"):
-        path = os.path.join(HERE, "_ref", "libcurrennt_ref%s.so" % ("_omp" if kind == "ref_omp" else ""))
+    if kind in ("ref", "ref_omp", "ref_b200"):
+        path = os.path.join(HERE, "_ref", "libcurrennt_ref%s.so" % {"ref": "", "ref_omp": "_omp", "ref_b200": "_b200"}[kind])
         if not os.path.exists(path):
             raise FileNotFoundError(path + " (run oracle/build_ref.sh where the reference checkout exists)")
-        lib, pre = C.CDLL(path), "ref_"
+        lib, pre = C.CDLL(path), ("refb200_" if kind == "ref_b200" else "ref_")
     else:
         name = "libcurrennt_oracle%s.so" % ("_f64" if kind == "port64" else "")
         path = os.path.join(HERE, name)

@@ -175,11 +175,13 @@ struct PtcBuffers {
     unsigned *maxbits = nullptr;                   // [2] largest |w| of the recurrent block per direction (float bits)
     float *scale = nullptr;                        // [direction][2]: S, 1/S
     uint4 *wimg_f = nullptr, *wimg_b = nullptr;    // per-block weight images of the forward / backward sweep
-    unsigned long long *xh = nullptr, *xe = nullptr;   // exchange words of the forward / backward sweep
+    unsigned char *xh = nullptr;                   // forward exchange: fp16 operand images of h, per chunk, step parity, slice
+    float *xe = nullptr;                           // backward exchange: partial output errors, per chunk, step parity, row tile
+    unsigned *flags = nullptr;                     // step counters the blocks publish to each other
 };
 bool lstm_ptc_supported(const LstmShape &s);
 size_t lstm_ptc_image_bytes(int els, int D);
-void lstm_ptc_exchange_words(int els, int P, int D, size_t *xh_words, size_t *xe_words);
+void lstm_ptc_exchange_sizes(int els, int P, int D, size_t *xh_bytes, size_t *xe_floats, size_t *flag_words);
 int lstm_ptc_prepare(const LstmShape &s, const float *w, const PtcBuffers &pb, cudaStream_t st);
 int lstm_ptc_sweep(bool backward, const LstmShape &s, const LstmBuffers &b, const PtcBuffers &pb, const float *w, float *y,
                    const float *dy, int *status, unsigned *tag_next, cudaStream_t st);

@@ -84,9 +84,9 @@ def assert_grads_close(layers, i, a, b, what):
         assert_rel_close(a[sl], b[sl], "%s layer %d %s" % (what, i, name))
 
 
-def compare_run(layers, got, want, what, lstm_pad_zero_lens=None, P=None):
+def compare_run(layers, got, want, what, lstm_pad_zero_lens=None, P=None, loss_rtol=1e-5):
     """got/want: dicts with loss, out<i>, dyin<i>, dw<i> (want may hold more keys)."""
-    assert abs(got["loss"] - want["loss"]) <= 1e-5 * abs(want["loss"]) + 1e-6, (what, got["loss"], want["loss"])
+    assert abs(got["loss"] - want["loss"]) <= loss_rtol * abs(want["loss"]) + 1e-6, (what, got["loss"], want["loss"])
     for i in range(1, len(layers)):
         if layers[i]["type"] == "sse":
             continue

@@ -150,7 +150,10 @@ def test_cfg1_fraction_at_full_size_against_the_reference():
     paths = {}
     got = run_gpu(wl["layers"], wl["P"], wl["lens"], wl["x"], wl["tg"], wl["weights"], dict(recurrence=1, ffma=0), paths=paths)
     print("cfg1 full size: recurrence paths", paths, "error", got["loss"], "reference", want["loss"])
-    parity.compare_run(wl["layers"], got, want, "cfg1 full size", lstm_pad_zero_lens=wl["lens"])
+    # The reference adds the 4.5 million squared differences of this fraction in fp32 (SsePostOutputLayer.cu:197-209);
+    # the library accumulates in double.  The error bound is widened to what fp32 accumulation of that many terms
+    # can lose; every other quantity keeps its bound.
+    parity.compare_run(wl["layers"], got, want, "cfg1 full size", lstm_pad_zero_lens=wl["lens"], loss_rtol=5e-4)
 
 
 @pytest.mark.parametrize("variant", VARIANTS[1:5] + VARIANTS[6:], ids=VARIANT_IDS[1:5] + VARIANT_IDS[6:])
