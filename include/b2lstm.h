@@ -151,6 +151,10 @@ typedef struct b2_net b2_net;
  * Weights absent from the JSON are drawn U(-0.08, 0.08)... by seed `random_seed`. */
 int b2_net_create(const char *network_json, int parallel_sequences, int max_seq_length, unsigned random_seed,
                   b2_net **out);
+/* --lstm_forget_gate_bias (Configuration.cpp:682-683, layers/LstmLayer.cu:1147-1161): a value above 1e-4 is added to
+ * every forget-gate bias of the (b)lstm layers that b2_net_create initialises at random from now on (layers whose
+ * weights come from the JSON are left alone).  Process-wide, like the reference's Configuration; default 0. */
+void b2_config_set_lstm_forget_gate_bias(float value);
 void b2_net_destroy(b2_net *net);
 /* Layer::parallelSequences() / Layer::maxSeqLength() (layers/Layer.hpp:163-175) the net was created with */
 int b2_net_parallel_sequences(const b2_net *net);

@@ -78,13 +78,21 @@ class _quiet_stdout:
 class OracleNet:
     """layers: list of dicts with keys type, size and (trainable layers) bias, as in network.jsn."""
 
-    def __init__(self, layers, P, maxT, kind="port"):
+    def __init__(self, layers, P, maxT, kind="port", weights_section=None):
+        """weights_section (reference kinds only): the "weights" object of a network file; the layers then read their
+        weights from it, as the reference does when it loads trained_network.jsn"""
         self.kind, self.layers, self.P, self.maxT = kind, layers, P, maxT
         self.lib, self.pre = _load(kind)
         if kind.startswith("ref"):
-            js = json.dumps({"layers": [dict({"name": "l%d" % i, "bias": 1.0}, **l) for i, l in enumerate(layers)]})
+            doc = {"layers": [dict({"name": "l%d" % i, "bias": 1.0}, **l) for i, l in enumerate(layers)]}
+            fn = "create"
+            if weights_section is not None:
+                doc["weights"] = weights_section
+                fn = "create_with_weights"
+                self._f(fn).restype = C.c_void_p
+            js = json.dumps(doc)
             with _quiet_stdout():
-                self.h = C.c_void_p(self._f("create")(js.encode(), P, maxT))
+                self.h = C.c_void_p(self._f(fn)(js.encode(), P, maxT))
             if not self.h:
                 self.lib.ref_last_error.restype = C.c_char_p
                 raise RuntimeError(self.lib.ref_last_error().decode())
@@ -112,6 +120,17 @@ class OracleNet:
 
     def num_weights(self, i):
         return int(self._f("num_weights")(self.h, i))
+
+    def export_json(self):
+        """the network document as the reference writes it: its layers' exportLayer / exportWeights and its own JSON writer"""
+        fn = self._f("export_json")
+        fn.restype = C.c_long
+        need = -int(fn(self.h, None, 0))
+        buf = C.create_string_buffer(need)
+        n = int(fn(self.h, buf, need))
+        if n <= 0:
+            raise RuntimeError("export_json failed")
+        return buf.value.decode()
 
     def set_weights(self, i, w):
         w = np.ascontiguousarray(w, np.float32)

@@ -30,6 +30,8 @@
 #include "LstmLayerB200.hpp"
 #endif
 #include <thrust/copy.h>
+#include "rapidjson/prettywriter.h"
+#include "rapidjson/stringbuffer.h"
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -239,6 +241,76 @@ struct RefNetT {
         std::copy(dY[i].begin(), dY[i].begin() + cnt, out);
         return (long)cnt;
     }
+    // The document NeuralNetwork::exportLayers / exportWeights / saveNetwork write (NeuralNetwork.cpp:2993-3043,4104-4125):
+    // every layer's own exportLayer and TrainableLayer::exportWeights (layers/TrainableLayer.cu:441-480) fill it, the
+    // reference's rapidjson PrettyWriter turns it into text, as in saveNetwork.  Returns the length (without NUL), or
+    // minus the needed capacity.
+    long export_json(char *buf, long cap) {
+        try {
+            rapidjson::Document d;
+            d.SetObject();
+            rapidjson::Value layersArray(rapidjson::kArrayType);
+            rapidjson::Value weightsObject(rapidjson::kObjectType);
+            for (size_t i = 0; i < layers.size(); ++i) {
+                layers[i]->exportLayer(&layersArray, &d.GetAllocator());
+                layers::TrainableLayer<TDevice> *t = trainable((int)i);
+                if (t) t->exportWeights(&weightsObject, &d.GetAllocator());
+            }
+            d.AddMember("layers", layersArray, d.GetAllocator());
+            d.AddMember("weights", weightsObject, d.GetAllocator());
+            rapidjson::StringBuffer sb;
+            rapidjson::PrettyWriter<rapidjson::StringBuffer> writer(sb);
+            d.Accept(writer);
+            const long n = (long)sb.Size();
+            if (n + 1 > cap) return -(n + 1);
+            memcpy(buf, sb.GetString(), (size_t)n);
+            buf[n] = 0;
+            return n;
+        } catch (const std::exception &e) {
+            snprintf(g_err, sizeof g_err, "%s", e.what());
+            return 0;
+        }
+    }
+    // a net whose trainable layers read their weights from the document's "weights" section, as the reference does
+    // when it continues from trained_network.jsn (TrainableLayer.cu:135-205)
+    static RefNetT *create_with_weights(const char *network_json, int P, int maxT) {
+        try {
+            if (!g_cfg) {
+                static const char *av[] = {"ref"};
+                g_cfg = new Configuration(1, av);
+            }
+            std::unique_ptr<RefNetT> n(new RefNetT);
+            n->P = P;
+            n->maxT = maxT;
+            if (n->doc.template Parse<0>(network_json).HasParseError()) throw std::runtime_error("bad network json");
+            rapidjson::Value &L = n->doc["layers"];
+            helpers::JsonValue weights;
+            if (n->doc.HasMember("weights")) weights = helpers::JsonValue(&n->doc["weights"]);
+            for (rapidjson::SizeType i = 0; i < L.Size(); ++i) {
+                std::string ty = L[i]["type"].GetString();
+                layers::Layer<TDevice> *lay = NULL;
+                if (i == 0) lay = new layers::InputLayer<TDevice>(&L[i], P, maxT, 0);
+                else {
+                    layers::Layer<TDevice> &prev = *n->layers.back();
+                    if (ty == "feedforward_tanh") lay = new layers::FeedForwardLayer<TDevice, ActTanh>(&L[i], weights, prev, maxT, (int)i);
+                    else if (ty == "feedforward_logistic") lay = new layers::FeedForwardLayer<TDevice, ActLogistic>(&L[i], weights, prev, maxT, (int)i);
+                    else if (ty == "feedforward_identity") lay = new layers::FeedForwardLayer<TDevice, ActIdentity>(&L[i], weights, prev, maxT, (int)i);
+                    else if (ty == "lstm") lay = new Lstm(&L[i], weights, prev, maxT, (int)i, false);
+                    else if (ty == "blstm") lay = new Lstm(&L[i], weights, prev, maxT, (int)i, true);
+                    else if (ty == "sse") lay = new layers::SsePostOutputLayer<TDevice>(&L[i], prev, maxT, (int)i);
+                    else throw std::runtime_error("unsupported layer type " + ty);
+                }
+                n->layers.emplace_back(lay);
+                n->types.push_back(ty);
+            }
+            n->dY.resize(n->layers.size());
+            n->momentum.resize(n->layers.size());
+            return n.release();
+        } catch (const std::exception &e) {
+            snprintf(g_err, sizeof g_err, "%s", e.what());
+            return NULL;
+        }
+    }
     // g <- 0 where NaN/Inf; delta <- momentum*delta - lr*g; w <- w + delta   (restated, see header); host vectors only
     void sgd_update(float lr, float mom) {
         for (size_t i = 0; i < layers.size(); ++i) {
@@ -281,7 +353,9 @@ struct RefNetT {
     long PFX##get_outputs(void *h, int i, float *out) { return ((NET *)h)->get_outputs(i, out); }                             \
     long PFX##get_output_errors(void *h, int i, float *out) { return ((NET *)h)->get_output_errors(i, out); }                 \
     long PFX##get_output_errors_in(void *h, int i, float *out) { return ((NET *)h)->get_output_errors_in(i, out); }           \
-    void PFX##sgd_update(void *h, float lr, float mom) { ((NET *)h)->sgd_update(lr, mom); }
+    void PFX##sgd_update(void *h, float lr, float mom) { ((NET *)h)->sgd_update(lr, mom); }                                   \
+    long PFX##export_json(void *h, char *buf, long cap) { return ((NET *)h)->export_json(buf, cap); }                         \
+    void *PFX##create_with_weights(const char *network_json, int P, int maxT) { return NET::create_with_weights(network_json, P, maxT); }
 
 extern "C" {
 

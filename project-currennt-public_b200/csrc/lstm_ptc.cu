@@ -61,8 +61,14 @@ constexpr unsigned POLL_LIMIT = 1u << 22;
 constexpr float LO_SCALE = 2048.0f, LO_UNSCALE = 1.0f / 2048.0f;
 constexpr uint32_t A_HALF = 32768, A_BYTES = 65536;   // weight image: hi, lo of 128 rows x 128 fp16
 
-constexpr int FWD_THREADS = 32 * 15;     // warp 0 MMA issue, 1 poll + operand fetch, 2-5 drain, 6-13 cell math, 14 publisher
-constexpr int BWD_THREADS = 32 * 14;     // warp 0 MMA issue, 1-4 cell math, 5-8 drain, 9-12 gather + reduce, 13 publisher
+// Warp roles.  Forward: warp 0 MMA issue, 1 poll + operand fetch, 2-5 drain, then the cell-math warps, last the publisher.
+// Backward: warp 0 MMA issue, then the cell-math warps, 4 drain warps, 4 gather + reduce warps, last the publisher.
+// With several chunks per group the cell math bounds the throughput, so that variant gets twice the cell warps; with
+// one chunk per group (LL) a step is a chain of latencies and fewer, fatter threads are as good.
+__host__ __device__ constexpr int fwd_cell_warps(bool ll) { return ll ? 8 : 16; }
+__host__ __device__ constexpr int bwd_cell_warps(bool ll) { return ll ? 4 : 8; }
+__host__ __device__ constexpr int fwd_threads(bool ll) { return 32 * (7 + fwd_cell_warps(ll)); }
+__host__ __device__ constexpr int bwd_threads(bool ll) { return 32 * (10 + bwd_cell_warps(ll)); }
 
 // Optional timing trace (build with -DB2_PTC_TRACE): block 0 records clock64() at the hand-over points of its
 // roles for the first chunk-steps of a launch; b2_debug_ptc_trace copies the records out.
@@ -191,9 +197,11 @@ __device__ __forceinline__ bool poll_flags(const unsigned *flags, int stride, un
 // forward
 // =====================================================================================================
 template <int ELS, int NC, bool LL>
-__global__ void __launch_bounds__(FWD_THREADS, 1) lstm_fwd_ptc_kernel(PtcArgs a) {
+__global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArgs a) {
     typedef Geo<ELS, NC> G;
-    constexpr int RT = G::RT, CPT = NC / 32;
+    constexpr int CW = fwd_cell_warps(LL), FWD_THREADS = fwd_threads(LL);
+    constexpr int RT = G::RT, CPT = NC / (4 * CW);   // a cell warp covers 8 units x 4 sequences
+    static_assert(CPT >= 1, "more cell warps than cells");
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) u64 bars[16];
     __shared__ uint32_t tmem_base_s;
@@ -221,10 +229,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) lstm_fwd_ptc_kernel(PtcArgs a)
 
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
-            mbar_init(b_full(b), LL ? 8 : 1); mbar_init(b_free(b), 1); mbar_init(acc_full(b), 1); mbar_init(acc_free(b), 4);
+            mbar_init(b_full(b), LL ? CW : 1); mbar_init(b_free(b), 1); mbar_init(acc_full(b), 1); mbar_init(acc_free(b), 4);
             mbar_init(z_full(b), 5);           // 4 drain warps + the arrival that announces the peers' bytes
-            mbar_init(z_free(b), 8 * KS);      // every cell warp of every block of the cluster
-            mbar_init(rel_full(b), 8); mbar_init(rel_free(b), 1);
+            mbar_init(z_free(b), CW * KS);     // every cell warp of every block of the cluster
+            mbar_init(rel_full(b), CW); mbar_init(rel_free(b), 1);
         }
         give_up_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) lstm_fwd_ptc_kernel(PtcArgs a)
                 }
                 __syncwarp();
             }
-        } else if (warp == 14) {
+        } else if (warp == 6 + CW) {
             // ------------------------------------ publisher: the block's step counter follows its h[t] ------------------------------------
             // The cell warps hand their stores over through a CTA-scope barrier; the release store at gpu scope is
             // cumulative over them.  Its fence waits for every global store of the block that is still in flight, which
@@ -425,6 +433,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) lstm_fwd_ptc_kernel(PtcArgs a)
             // published their own part: no release fence at the producers, no counter round trip, no bulk-copy start-up.
             // sprev: the step whose h is collected; buf / ph: buffer and barrier phase of the chunk-step that consumes it.
             auto gather_ll = [&](int sprev, int ac, int buf, uint32_t ph) {
+                static_assert(!LL || CW == 8, "the collecting code is laid out for 256 threads");
                 constexpr int CH = NC * 16 / 256;   // 16-byte operand chunks (8 source units of one sequence) per thread
                 bool okg = mbar_wait_bounded<false>(b_free(buf), ph ^ 1u, &give_up_s, WAIT_CYCLES);
                 const u64 *src = reinterpret_cast<const u64 *>(a.xh) + ((dch + ac) * 2 + (sprev & 1)) * (size_t)(NC * ELS) + KSL * q;
@@ -594,7 +603,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) lstm_fwd_ptc_kernel(PtcArgs a)
             // frames beyond a chunk's longest sequence are padding for all its sequences: outputs are zero there
             for (int c2 = 0; c2 < ncl; ++c2) {
                 const int p0 = (sl + c2 * a.nslices) * NC;
-                for (int i = slot; i < (T - Tc_s[c2]) * NC; i += 32) {
+                for (int i = slot; i < (T - Tc_s[c2]) * NC; i += 4 * CW) {
                     const int t = Tc_s[c2] + i / NC, pg = p0 + i % NC;
                     if (pg < P) a.y[((size_t)t * P + pg) * ls + u] = 0.0f;
                 }
@@ -615,9 +624,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) lstm_fwd_ptc_kernel(PtcArgs a)
 // backward
 // =====================================================================================================
 template <int ELS, int NC, bool LL>
-__global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a) {
+__global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArgs a) {
     typedef Geo<ELS, NC> G;
-    constexpr int RT = G::RT, CPT = NC / 16;
+    constexpr int CW = bwd_cell_warps(LL), BWD_THREADS = bwd_threads(LL), CT = 32 * CW;
+    constexpr int RT = G::RT, CPT = NC / (4 * CW);   // a cell warp covers 8 units x 4 sequences
+    static_assert(CPT >= 1, "more cell warps than cells");
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) u64 bars[16];
     __shared__ uint32_t tmem_base_s;
@@ -646,7 +657,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
             mbar_init(b_full(b), 1); mbar_init(b_free(b), KS); mbar_init(acc_full(b), 1); mbar_init(acc_free(b), 4);
-            mbar_init(e_full(b), 4); mbar_init(e_free(b), 4);
+            mbar_init(e_full(b), 4); mbar_init(e_free(b), CW);
             mbar_init(rel_full(b), 4); mbar_init(rel_free(b), 1);
         }
         give_up_s = 0;
@@ -711,7 +722,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
                     PTC_TRACE_B(0, ti, 2);
                 }
             }
-        } else if (warp <= 4) {
+        } else if (warp <= CW) {
             // ------------------------------------------------ cell math: the error functor ------------------------------------------------
             const int et = tid - 32;
             const int jj = et & 7, slot = et >> 3;           // unit jj of this block, sequences slot*CPT .. +CPT
@@ -793,8 +804,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
                     // operand buffer pbuf: the MMAs of the chunk-step before last, in every block of the cluster, have read it
                     if (ok) ok = mbar_wait_bounded<true>(b_free(pbuf), pph ^ 1u, &give_up_s, WAIT_CYCLES);
                 }
-                // the 128 threads leave together or not at all (named barriers follow)
-                if (bar_named_or(1, 128, !ok)) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
+                // the cell threads leave together or not at all (named barriers follow)
+                if (bar_named_or(1, CT, !ok)) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
                 if (et == 0) PTC_TRACE_B(1, ti, 2);
                 float *ce_cur = a.bf.cerr + (size_t)(s & 1) * P * ls;
 #pragma unroll
@@ -830,11 +841,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
                 }
                 if (et == 0) PTC_TRACE_B(1, ti, 3);
                 if (feeds) {
-                    bar_named(1, 128);
+                    bar_named(1, CT);
                     // 16-byte operand chunks (the 8 units of one gate and sequence) into this block's operand B and the peers'
                     const uint32_t bb = sbase + G::B_B + (uint32_t)pbuf * G::B_BUF;
                     constexpr int NCHUNK = 2 * NC * 4;
-                    for (int ci = et; ci < NCHUNK; ci += 128) {
+                    for (int ci = et; ci < NCHUNK; ci += CT) {
                         const int g = ci & 3, n = (ci >> 2) % NC, hl = ci / (4 * NC);
                         const uint4 v = *reinterpret_cast<const uint4 *>(dstage + (hl * NC + n) * (4 * UPC) + g * UPC);
                         const int clc = g * 4 + q;   // chunk index along the 128 gate rows of the row tile
@@ -846,7 +857,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
                             if (pr != q) st_async_v4(map_to_rank(bb + o, (uint32_t)pr), v.x, v.y, v.z, v.w, map_to_rank(b_full(pbuf), (uint32_t)pr));
                     }
                     fence_async_smem();
-                    bar_named(1, 128);
+                    bar_named(1, CT);
                     // one arrival per phase; it also announces the bytes the peers deliver into this buffer
                     if (et == 0) mbar_expect_tx(b_full(pbuf), (uint32_t)(KS - 1) * 2u * NC * 4u * UPC * 2u);
                 }
@@ -858,7 +869,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
             // frames beyond a chunk's longest sequence: zero deltas (they are operands of the gradient GEMMs)
             for (int c2 = 0; c2 < ncl; ++c2) {
                 const int p0 = (sl + c2 * a.nslices) * NC;
-                for (int i = slot; i < (T - Tc_s[c2]) * NC; i += 16) {
+                for (int i = slot; i < (T - Tc_s[c2]) * NC; i += 4 * CW) {
                     const int t = Tc_s[c2] + i / NC, pg = p0 + i % NC;
                     if (pg < P) {
                         const size_t o = ((size_t)t * P + pg) * 4 * ls + u;
@@ -866,7 +877,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
                     }
                 }
             }
-        } else if (warp <= 8) {
+        } else if (warp <= CW + 4) {
             // ------------------------------------------------ drain: partial output errors to global memory ------------------------------------------------
             const int q4 = warp & 3;
             const uint32_t lane_base = tmem + ((uint32_t)(32 * q4) << 16);
@@ -879,13 +890,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
                 const int ti = mp_d;
                 (void)ti;
                 ++mp_d;
-                if (warp == 5 && lane == 0) PTC_TRACE_B(3, ti, 0);
+                if (warp == CW + 1 && lane == 0) PTC_TRACE_B(3, ti, 0);
                 const bool ok = mbar_wait_bounded<false>(acc_full(buf), ph, &give_up_s, WAIT_CYCLES);
-                if (warp == 5 && lane == 0) PTC_TRACE_B(3, ti, 1);
+                if (warp == CW + 1 && lane == 0) PTC_TRACE_B(3, ti, 1);
                 if (!__all_sync(0xffffffffu, ok)) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
                 tc_fence_after();
                 // the MMAs of this chunk-step are complete: the peers may refill their copy of operand buffer buf
-                if (warp == 5 && lane < KS && lane != q) mbar_arrive_cluster_relaxed(map_to_rank(b_free(buf), (uint32_t)lane));
+                if (warp == CW + 1 && lane < KS && lane != q) mbar_arrive_cluster_relaxed(map_to_rank(b_free(buf), (uint32_t)lane));
                 const int ac = sl + cl * a.nslices;
                 const size_t xoff = (((dch + ac) * 2 + (s & 1)) * RT + r) * (size_t)(NC * ELS) + KSL * q + 32 * q4 + lane;
 #pragma unroll
@@ -904,7 +915,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (warp == 5 && lane == 0) PTC_TRACE_B(3, ti, 2);
+                if (warp == CW + 1 && lane == 0) PTC_TRACE_B(3, ti, 2);
                 if (lane == 0) {
                     mbar_arrive(acc_free(buf));
                     if (!LL) {
@@ -914,7 +925,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
                     }
                 }
             }
-        } else if (warp == 13) {
+        } else if (warp == CW + 9) {
             // ------------------------------------ publisher: the block's step counter follows its partial errors ------------------------------------
             int s = 0, cl = -1;
             while (!LL && next_item(s, cl, ncl, Tc_s, Tmax)) {
@@ -933,7 +944,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) lstm_bwd_ptc_kernel(PtcArgs a)
             }
         } else {
             // ------------------------------------------------ gather + reduce the partial output errors ------------------------------------------------
-            const int rt = tid - 288;
+            const int rt = tid - 32 * (CW + 5);
             float *esum = reinterpret_cast<float *>(gbase + G::B_ESUM);
             const int n = rt >> 1, hf = rt & 1;          // sequence n, units 4*hf .. 4*hf+3 of this block
             const bool active = n < NC;
@@ -1126,7 +1137,7 @@ int launch(bool backward, PtcArgs &a, const Plan &pl, cudaStream_t st) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = KS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.gridDim = dim3(pl.groups * G::GROUP);
-    cfg.blockDim = dim3(backward ? BWD_THREADS : FWD_THREADS);
+    cfg.blockDim = dim3(backward ? bwd_threads(LL) : fwd_threads(LL));
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cfg.attrs = attr;

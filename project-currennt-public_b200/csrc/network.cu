@@ -17,6 +17,7 @@ namespace b2 {
 // ---- status ---------------------------------------------------------------------------------------
 static thread_local char g_err[1024] = "";
 unsigned long long g_launches = 0;
+float g_lstm_forget_gate_bias = 0.0f;   // the process-wide option, like the reference's Configuration singleton
 
 void set_error(const char *fmt, ...) {
     va_list ap;
@@ -374,6 +375,13 @@ int NeuralNetwork::create(const char *networkJson, int P_, int maxT_, unsigned s
             }
         } else {
             for (size_t k = 0; k < w.size(); ++k) w[k] = dist(gen);
+            // --lstm_forget_gate_bias (Configuration.cpp:682-683): freshly initialised (b)lstm layers get the value added
+            // to every forget-gate bias (layers/LstmLayer.cu:1147-1161); layers read from a weights section do not
+            LstmLayer *l = dynamic_cast<LstmLayer *>(t);
+            if (l && g_lstm_forget_gate_bias > 0.0001f) {
+                const size_t ls = (size_t)l->size(), pls = (size_t)l->precedingLayer()->size();
+                for (size_t k = 0; k < ls; ++k) w[4 * ls * pls + 2 * ls + k] += g_lstm_forget_gate_bias;
+            }
         }
         B2_CUDA(cudaMemcpy(t->weights(), w.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice));
     }
@@ -677,6 +685,7 @@ int b2_net_create(const char *network_json, int P, int maxT, unsigned seed, b2_n
     return B2_OK;
 }
 void b2_net_destroy(b2_net *n) { delete n; }
+void b2_config_set_lstm_forget_gate_bias(float value) { b2::g_lstm_forget_gate_bias = value; }
 int b2_selftest_inject_status(b2_net *n, int code) {
     if (!n) return B2_ERR_BAD_ARG;
     B2_CUDA(cudaStreamSynchronize(n->net.stream));

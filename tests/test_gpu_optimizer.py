@@ -215,3 +215,105 @@ def test_batch_learning_sums_the_epoch_and_updates_once(tmp_path):
         assert np.allclose(net.get_weights(i), want, rtol=1e-5, atol=1e-7)
         assert np.allclose(net.weight_deltas(i), -np.float32(lr) * gsum[i], rtol=1e-4, atol=1e-9)
     net.close()
+
+
+def test_forget_gate_bias_option_shifts_only_the_forget_biases_of_fresh_lstm_layers():
+    """--lstm_forget_gate_bias of the reference (layers/LstmLayer.cu:1147-1161): the value is added to the forget-gate
+    biases of randomly initialised (b)lstm layers and to nothing else; layers read from a weights section keep theirs."""
+    import b2lstm
+    from b2lstm.lib import lib
+    layers = [dict(type="input", size=5), dict(type="feedforward_tanh", size=6, bias=1.0), dict(type="blstm", size=8, bias=1.0),
+              dict(type="lstm", size=3, bias=1.0), dict(type="feedforward_identity", size=2, bias=1.0), dict(type="sse", size=2)]
+    plain = b2lstm.Net(layers, 2, 4, seed=77)
+    w0 = {i: plain.get_weights(i) for i in (1, 2, 3, 4)}
+    plain.close()
+    lib().b2_config_set_lstm_forget_gate_bias(1.5)
+    try:
+        shifted = b2lstm.Net(layers, 2, 4, seed=77)
+        w1 = {i: shifted.get_weights(i) for i in (1, 2, 3, 4)}
+        shifted.close()
+        sizes = {1: (6, 5, 1), 2: (8, 6, 4), 3: (3, 8, 4), 4: (2, 3, 1)}      # layer: (size, preceding size, input weights per unit)
+        section = {}
+        for i, (ls, pls, per) in sizes.items():
+            n_in, n_b = per * ls * pls, per * ls
+            section["l%d" % i] = {"input": w0[i][:n_in].tolist(), "bias": w0[i][n_in:n_in + n_b].tolist(),
+                                  "internal": w0[i][n_in + n_b:].tolist()}
+        given = b2lstm.Net(layers, 2, 4, seed=77, weights=section)     # weights from the JSON section: untouched
+        w2 = {i: given.get_weights(i) for i in (1, 2, 3, 4)}
+        given.close()
+    finally:
+        lib().b2_config_set_lstm_forget_gate_bias(0.0)
+    for i, (ls, pls) in {2: (8, 6), 3: (3, 8)}.items():
+        d = w1[i] - w0[i]
+        lo = 4 * ls * pls + 2 * ls
+        assert np.allclose(d[lo:lo + ls], 1.5) and not d[:lo].any() and not d[lo + ls:].any()
+    for i in (1, 4):
+        assert np.array_equal(w1[i], w0[i])
+    for i in (1, 2, 3, 4):
+        assert np.array_equal(w2[i], w0[i])
+
+
+def _mixed_net():
+    from b2lstm import workloads
+    layers = [dict(type="input", size=5), dict(type="feedforward_tanh", size=6, bias=1.0), dict(type="blstm", size=8, bias=0.5),
+              dict(type="lstm", size=3, bias=1.0), dict(type="feedforward_identity", size=2, bias=1.0), dict(type="sse", size=2)]
+    return layers, workloads.make_weights(layers, 5, 0.3)
+
+
+def test_export_equals_what_the_reference_writes():
+    """The network document against the reference's own writer: Layer::exportLayer, TrainableLayer::exportWeights
+    (layers/TrainableLayer.cu:441-480) and its rapidjson PrettyWriter, run on the same weights.  Same layer entries,
+    same section split (input | bias | internal) and, at the reference's 6 significant digits, the same numbers."""
+    import b2lstm
+    from oracle import OracleNet, ref_available
+    if not ref_available():
+        pytest.skip("the reference library (oracle/_ref) did not travel with the repository")
+    layers, w = _mixed_net()
+    ref = OracleNet(layers, 2, 4, "ref")
+    net = b2lstm.Net(layers, 2, 4)
+    for i, wi in w.items():
+        ref.set_weights(i, wi)
+        net.set_weights(i, wi)
+    want = json.loads(ref.export_json())
+    got = json.loads(net.export_json(digits=6))
+    ref.close()
+    net.close()
+    assert [l["name"] for l in got["layers"]] == [l["name"] for l in want["layers"]]
+    for a, b in zip(got["layers"], want["layers"]):
+        for key in ("type", "size", "bias"):
+            assert a.get(key) == b.get(key), (a, b)
+    assert sorted(got["weights"]) == sorted(want["weights"])
+    for name, sec in want["weights"].items():
+        for part in ("input", "bias", "internal"):
+            assert got["weights"][name][part] == sec[part], (name, part)
+
+
+def test_network_files_travel_between_the_two_implementations():
+    """A document the reference wrote is read by b2_net_create, and a document this library wrote (9 digits: exact for
+    fp32) is read by the reference's TrainableLayer constructor (layers/TrainableLayer.cu:135-205)."""
+    import b2lstm
+    from oracle import OracleNet, ref_available
+    if not ref_available():
+        pytest.skip("the reference library (oracle/_ref) did not travel with the repository")
+    layers, w = _mixed_net()
+    ref = OracleNet(layers, 2, 4, "ref")
+    for i, wi in w.items():
+        ref.set_weights(i, wi)
+    doc = json.loads(ref.export_json())
+    ref.close()
+    net = b2lstm.Net(layers, 2, 4, weights=doc["weights"])
+    for i in w:
+        sec = doc["weights"]["l%d" % i]
+        written = np.array(sec["input"] + sec["bias"] + sec["internal"], np.float32)
+        assert np.array_equal(net.get_weights(i), written)
+        assert np.allclose(written, w[i], rtol=1e-5, atol=0)
+    net.close()
+    net = b2lstm.Net(layers, 2, 4)
+    for i, wi in w.items():
+        net.set_weights(i, wi)
+    doc = json.loads(net.export_json())
+    net.close()
+    back = OracleNet(layers, 2, 4, "ref", weights_section=doc["weights"])
+    for i in w:
+        assert np.array_equal(back.get_weights(i), w[i])
+    back.close()
