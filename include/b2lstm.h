@@ -99,6 +99,10 @@ void b2_lstm_destroy(b2_lstm *layer);
  * fraction's shape.  pat_types_dev: device char[cur_max_len * P]; padding frames (type 0) must trail
  * their sequence, as data_sets::DataSet writes them. */
 int b2_lstm_load_sequences(b2_lstm *layer, int cur_max_len, int cur_min_len, const char *pat_types_dev);
+/* Non-zero makes b2_lstm_load_sequences verify that contract on the device (B2_ERR_BAD_ARG when a real frame follows a
+ * padding frame) at the price of one device round trip per fraction; off by default.  The reference needs no such
+ * check: it reads the pattern type of every frame (layers/LstmLayer.cu:89-101). */
+int b2_lstm_set_check_padding(b2_lstm *layer, int on);
 /* LstmLayer::computeForwardPass (LstmLayer.cu:1744-1949).
  * weights_dev: b2_lstm_num_weights floats; x_dev: prev_size x (T*P) = precedingLayer().outputs();
  * y_dev: size x (T*P) = outputs(), forward-direction units first, then backward-direction units.

@@ -40,6 +40,7 @@ SIGNATURES = {
     "b2_lstm_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b2_lstm_backward": (C.c_int, [C.c_void_p] * 8),
     "b2_lstm_set_recurrence_mode": (C.c_int, [C.c_void_p, C.c_int]),
+    "b2_lstm_set_check_padding": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_lstm_state_bytes": (C.c_size_t, [C.c_void_p]),
     "b2_lstm_recurrence_path": (C.c_int, [C.c_void_p, C.c_int]),
     "b2_net_recurrence_path": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
@@ -208,6 +209,9 @@ class LstmLayer:
 
     def recurrence_path(self, backward=False):
         return int(lib().b2_lstm_recurrence_path(self.h, int(backward)))
+
+    def set_check_padding(self, on):
+        _check(lib().b2_lstm_set_check_padding(self.h, int(on)))
 
     @property
     def state_bytes(self):

@@ -65,7 +65,8 @@ int LstmLayerImpl::create(const b2_lstm_desc &d) {
 
 void LstmLayerImpl::destroy() {
     cudaFree(bufs.acts); cudaFree(bufs.cells); cudaFree(bufs.deltas); cudaFree(bufs.cerr); cudaFree(bufs.wrecT);
-    cudaFree(ws); cudaFree(xchg); cudaFree(status_dev);
+    cudaFree(ws); cudaFree(xchg); cudaFree(status_dev); cudaFree(pad_dev);
+    pad_dev = nullptr;
     cudaFree(tcrec.wrec_hi); cudaFree(tcrec.wrec_lo); cudaFree(tcrec.y_hi); cudaFree(tcrec.y_lo);
     cudaFree(tcrec.d_hi); cudaFree(tcrec.d_lo); cudaFree(tcrec.part);
     tcrec = TcRecBuffers();
@@ -83,10 +84,35 @@ LstmShape LstmLayerImpl::shape() const {
     return s;
 }
 
+namespace {
+// one thread per sequence slot: a padding frame (type NONE) followed by a frame that is not one
+__global__ void padding_trails_kernel(const char *pat, int T, int P, int *bad) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= P) return;
+    for (int t = 0; t + 1 < T; ++t)
+        if (pat[(size_t)t * P + p] == PAT_NONE && pat[(size_t)(t + 1) * P + p] != PAT_NONE) { atomicExch(bad, t + 1); return; }
+}
+}  // namespace
+
 int LstmLayerImpl::load_sequences(int cur_max, int cur_min, const char *pat) {
     if (cur_max <= 0 || cur_max > desc.max_seq_length || cur_min < 0 || cur_min > cur_max || !pat) {
         set_error("b2_lstm_load_sequences: lengths %d/%d outside 1..%d", cur_max, cur_min, desc.max_seq_length);
         return B2_ERR_BAD_SHAPE;
+    }
+    if (check_padding) {
+        // The persistent kernels find a sequence's padding once per sweep and rely on it trailing the sequence, as
+        // data_sets::DataSet writes it; the reference tests every frame (layers/LstmLayer.cu:89-101).  The check costs
+        // a device round trip per fraction, hence optional.
+        if (!pad_dev) B2_CUDA(cudaMalloc(&pad_dev, sizeof(int)));
+        B2_CUDA(cudaMemset(pad_dev, 0, sizeof(int)));
+        padding_trails_kernel<<<(desc.parallel_sequences + 127) / 128, 128>>>(pat, cur_max, desc.parallel_sequences, pad_dev);
+        count_launch();
+        int bad = 0;
+        B2_CUDA(cudaMemcpy(&bad, pad_dev, sizeof(int), cudaMemcpyDeviceToHost));
+        if (bad) {
+            set_error("b2_lstm_load_sequences: a real frame follows a padding frame (timestep %d): padding must trail its sequence", bad);
+            return B2_ERR_BAD_ARG;
+        }
     }
     T = cur_max; Tmin = cur_min; bufs.pat = pat;
     forward_done = false;
@@ -395,6 +421,12 @@ int b2_lstm_backward(b2_lstm *l, const float *w, const float *x, const float *y,
                      float *dw, b2_stream st) {
     if (!l) return B2_ERR_BAD_ARG;
     return l->impl.backward(w, x, y, dy, dx, dw, (cudaStream_t)st);
+}
+
+int b2_lstm_set_check_padding(b2_lstm *l, int on) {
+    if (!l) return B2_ERR_BAD_ARG;
+    l->impl.check_padding = on != 0;
+    return B2_OK;
 }
 
 int b2_lstm_set_recurrence_mode(b2_lstm *l, int mode) {

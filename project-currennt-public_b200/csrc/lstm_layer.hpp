@@ -11,6 +11,8 @@ struct LstmLayerImpl {
     bool forward_done = false;
     int recurrence_mode = 1;   // 0 stepwise, 1 persistent
     bool force_ffma = false;
+    bool check_padding = false;   // load_sequences verifies that padding frames trail their sequences
+    int *pad_dev = nullptr;       // result word of that check
     LstmBuffers bufs{};
     float *ws = nullptr;       // scratch: split-K partials, vector-gradient partials
     size_t ws_floats = 0;

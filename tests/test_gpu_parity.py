@@ -396,6 +396,24 @@ def test_tensor_core_gemm_keeps_fp32_accuracy_on_long_contractions():
         assert errs[0] < 2e-6 and errs[0] < 8 * errs[1] + 2e-7, errs
 
 
+def test_padding_that_does_not_trail_its_sequence_is_refused_when_the_check_is_on():
+    import torch
+    import b2lstm
+    P, T = 3, 6
+    layer = b2lstm.LstmLayer(P, T, 4, 6, True, 1.0)
+    pat = np.full((T, P), 2, np.int8)
+    pat[4:, 1] = 0                               # sequence 1: padding from frame 4 on (fine)
+    good = torch.from_numpy(pat.copy()).cuda()
+    pat[2, 2] = 0                                # sequence 2: a padding frame in the middle
+    bad = torch.from_numpy(pat).cuda()
+    layer.load_sequences(T, 4, bad)              # unchecked by default, as before
+    layer.set_check_padding(True)
+    layer.load_sequences(T, 4, good)
+    with pytest.raises(b2lstm.B2Error, match="padding must trail"):
+        layer.load_sequences(T, 4, bad)
+    layer.close()
+
+
 def test_errors_are_status_codes():
     import b2lstm
     layers = L(("input", 4), ("lstm", 4), ("sse", 4))
