@@ -61,14 +61,16 @@ constexpr unsigned POLL_LIMIT = 1u << 22;
 constexpr float LO_SCALE = 2048.0f, LO_UNSCALE = 1.0f / 2048.0f;
 constexpr uint32_t A_HALF = 32768, A_BYTES = 65536;   // weight image: hi, lo of 128 rows x 128 fp16
 
-// Warp roles.  Forward: warp 0 MMA issue, 1 poll + operand fetch, 2-5 drain, then the cell-math warps, last the publisher.
-// Backward: warp 0 MMA issue, then the cell-math warps, 4 drain warps, 4 gather + reduce warps, last the publisher.
+// Warp roles.  Forward: warp 0 MMA issue, 1 poll + operand fetch, 2-5 drain, then the cell-math warps, the publisher, and
+// a second MMA-issue warp.  Backward: warp 0 MMA issue, then the cell-math warps, 4 drain warps, 4 gather + reduce warps,
+// the publisher, and a second MMA-issue warp.  Two issuers: measured with a probe, 24 MMAs cost one issuing thread 1870
+// cycles, two threads of different warps (12 each, accumulators of their own) 940.
 // With several chunks per group the cell math bounds the throughput, so that variant gets twice the cell warps; with
 // one chunk per group (LL) a step is a chain of latencies and fewer, fatter threads are as good.
 __host__ __device__ constexpr int fwd_cell_warps(bool ll) { return ll ? 8 : 16; }
 __host__ __device__ constexpr int bwd_cell_warps(bool ll) { return ll ? 4 : 8; }
-__host__ __device__ constexpr int fwd_threads(bool ll) { return 32 * (7 + fwd_cell_warps(ll)); }
-__host__ __device__ constexpr int bwd_threads(bool ll) { return 32 * (10 + bwd_cell_warps(ll)); }
+__host__ __device__ constexpr int fwd_threads(bool ll) { return 32 * (8 + fwd_cell_warps(ll)); }
+__host__ __device__ constexpr int bwd_threads(bool ll) { return 32 * (11 + bwd_cell_warps(ll)); }
 
 // Optional timing trace (build with -DB2_PTC_TRACE): block 0 records clock64() at the hand-over points of its
 // roles for the first chunk-steps of a launch; b2_debug_ptc_trace copies the records out.
@@ -229,7 +231,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
 
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
-            mbar_init(b_full(b), LL ? CW : 1); mbar_init(b_free(b), 1); mbar_init(acc_full(b), 1); mbar_init(acc_free(b), 4);
+            mbar_init(b_full(b), LL ? CW : 1); mbar_init(b_free(b), 2); mbar_init(acc_full(b), 2); mbar_init(acc_free(b), 4);
             mbar_init(z_full(b), 5);           // 4 drain warps + the arrival that announces the peers' bytes
             mbar_init(z_free(b), CW * KS);     // every cell warp of every block of the cluster
             mbar_init(rel_full(b), CW); mbar_init(rel_free(b), 1);
@@ -237,7 +239,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
         give_up_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) tmem_alloc(smem_u32(&tmem_base_s), 256);
+    if (warp == 0) tmem_alloc(smem_u32(&tmem_base_s), 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -257,9 +259,10 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
         const float invS = a.scale[2 * d + 1];
         const size_t dch = (size_t)d * a.nchunks;
 
-        if (warp == 0) {
-            // ------------------------------------------------ MMA issue ------------------------------------------------
+        if (warp == 0 || warp == 7 + CW) {
+            // ------------------------------------------------ MMA issue (two warps, half of the k-steps each) ------------------------------------------------
             if (lane == 0) {
+                const int hh = warp == 0 ? 0 : 1;
                 const uint32_t idesc = idesc_f16(128, NC);
                 int s = 0, cl = -1;
                 while (next_item(s, cl, ncl, Tc_s, Tmax)) {
@@ -270,30 +273,32 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                     const int ti = m_m;
                     (void)ti;
                     ++m_m;
-                    PTC_TRACE(0, ti, 0);
+                    if (hh == 0) PTC_TRACE(0, ti, 0);
                     if (!mbar_wait_bounded<false>(b_full(buf), ph, &give_up_s, WAIT_CYCLES) ||
                         !mbar_wait_bounded<false>(acc_free(buf), ph ^ 1u, &give_up_s, WAIT_CYCLES)) {
                         give_up_s = 1;
                         break;
                     }
-                    PTC_TRACE(0, ti, 1);
+                    if (hh == 0) PTC_TRACE(0, ti, 1);
                     if (LL) fence_async_smem();
                     tc_fence_after();
-                    const uint32_t acc = tmem + (uint32_t)buf * 128u;
+                    // accumulators of buffer buf: [main | cross] of issuer 0, then of issuer 1, 64 columns each
+                    const uint32_t acc = tmem + (uint32_t)(buf * 256 + hh * 128);
                     const uint32_t bb = sbase + G::F_B + (uint32_t)buf * G::B_BUF;
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const int ks = 4 * hh + k4;
                         const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
                         const uint32_t bo = (uint32_t)(ks >> 2) * (NC * 128u) + (uint32_t)(ks & 3) * 32u;
                         const u64 ahi = desc_kmajor_sw128(sbase + ao, 1024), alo = desc_kmajor_sw128(sbase + A_HALF + ao, 1024);
                         const u64 bhi = desc_kmajor_sw128(bb + bo, 1024), blo = desc_kmajor_sw128(bb + G::B_HL + bo, 1024);
-                        mma_f16(acc + 64u, alo, bhi, idesc, ks ? 1u : 0u);
+                        mma_f16(acc + 64u, alo, bhi, idesc, k4 ? 1u : 0u);
                         mma_f16(acc + 64u, ahi, blo, idesc, 1u);
-                        mma_f16(acc, ahi, bhi, idesc, ks ? 1u : 0u);
+                        mma_f16(acc, ahi, bhi, idesc, k4 ? 1u : 0u);
                     }
                     mma_commit(b_free(buf));
                     mma_commit(acc_full(buf));
-                    PTC_TRACE(0, ti, 2);
+                    if (hh == 0) PTC_TRACE(0, ti, 2);
                 }
             }
         } else if (warp == 1) {
@@ -372,13 +377,17 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                 const uint32_t rbar = map_to_rank(z_full(buf), (uint32_t)tr);
 #pragma unroll
                 for (int col = 0; col < NC; col += 16) {
-                    uint32_t mn[16], cx[16];
-                    tmem_ld16(lane_base + (uint32_t)(buf * 128 + col), mn);
-                    tmem_ld16(lane_base + (uint32_t)(buf * 128 + 64 + col), cx);
+                    uint32_t mn[16], cx[16], mn1[16], cx1[16];
+                    tmem_ld16(lane_base + (uint32_t)(buf * 256 + col), mn);
+                    tmem_ld16(lane_base + (uint32_t)(buf * 256 + 64 + col), cx);
+                    tmem_ld16(lane_base + (uint32_t)(buf * 256 + 128 + col), mn1);
+                    tmem_ld16(lane_base + (uint32_t)(buf * 256 + 192 + col), cx1);
                     tmem_ld_wait();
                     float v[16];
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) v[c] = (__uint_as_float(mn[c]) + __uint_as_float(cx[c]) * LO_UNSCALE) * invS;
+                    for (int c = 0; c < 16; ++c)
+                        v[c] = ((__uint_as_float(mn[c]) + __uint_as_float(mn1[c])) +
+                                (__uint_as_float(cx[c]) + __uint_as_float(cx1[c])) * LO_UNSCALE) * invS;
 #pragma unroll
                     for (int qd = 0; qd < 4; ++qd) {
                         const int o = ((gate * (NC / 4) + (col >> 2) + qd) * UPC + tj) * 4;   // floats
@@ -617,7 +626,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
     if (give_up_s && tid == 0) atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT);
     // nobody leaves while a peer may still write into its shared memory
     cluster_sync_all();
-    if (warp == 0) tmem_dealloc(tmem, 256);
+    if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 // =====================================================================================================
@@ -656,14 +665,15 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
 
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
-            mbar_init(b_full(b), 1); mbar_init(b_free(b), KS); mbar_init(acc_full(b), 1); mbar_init(acc_free(b), 4);
+            mbar_init(b_full(b), 1); mbar_init(b_free(b), KS + 1);   // two local MMA issuers + the other three blocks' drains
+            mbar_init(acc_full(b), 2); mbar_init(acc_free(b), 4);
             mbar_init(e_full(b), 4); mbar_init(e_free(b), CW);
             mbar_init(rel_full(b), 4); mbar_init(rel_free(b), 1);
         }
         give_up_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) tmem_alloc(smem_u32(&tmem_base_s), 256);
+    if (warp == 0) tmem_alloc(smem_u32(&tmem_base_s), 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -683,9 +693,10 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
         const float invS = a.scale[2 * d + 1];
         const size_t dch = (size_t)d * a.nchunks;
 
-        if (warp == 0) {
-            // ------------------------------------------------ MMA issue ------------------------------------------------
+        if (warp == 0 || warp == CW + 10) {
+            // ------------------------------------------------ MMA issue (two warps, half of the k-steps each) ------------------------------------------------
             if (lane == 0) {
+                const int hh = warp == 0 ? 0 : 1;
                 const uint32_t idesc = idesc_f16(128, NC);
                 int s = 0, cl = -1;
                 while (next_item(s, cl, ncl, Tc_s, Tmax)) {
@@ -696,30 +707,31 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                     const int ti = mp_m;
                     (void)ti;
                     ++mp_m;
-                    PTC_TRACE_B(0, ti, 0);
+                    if (hh == 0) PTC_TRACE_B(0, ti, 0);
                     if (!mbar_wait_bounded<true>(b_full(buf), ph, &give_up_s, WAIT_CYCLES) ||
                         !mbar_wait_bounded<false>(acc_free(buf), ph ^ 1u, &give_up_s, WAIT_CYCLES)) {
                         give_up_s = 1;
                         break;
                     }
-                    PTC_TRACE_B(0, ti, 1);
+                    if (hh == 0) PTC_TRACE_B(0, ti, 1);
                     fence_async_smem();
                     tc_fence_after();
-                    const uint32_t acc = tmem + (uint32_t)buf * 128u;
+                    const uint32_t acc = tmem + (uint32_t)(buf * 256 + hh * 128);
                     const uint32_t bb = sbase + G::B_B + (uint32_t)buf * G::B_BUF;
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const int ks = 4 * hh + k4;
                         const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
                         const uint32_t bo = (uint32_t)(ks >> 2) * (NC * 128u) + (uint32_t)(ks & 3) * 32u;
                         const u64 ahi = desc_kmajor_sw128(sbase + ao, 1024), alo = desc_kmajor_sw128(sbase + A_HALF + ao, 1024);
                         const u64 bhi = desc_kmajor_sw128(bb + bo, 1024), blo = desc_kmajor_sw128(bb + G::B_HL + bo, 1024);
-                        mma_f16(acc + 64u, alo, bhi, idesc, ks ? 1u : 0u);
+                        mma_f16(acc + 64u, alo, bhi, idesc, k4 ? 1u : 0u);
                         mma_f16(acc + 64u, ahi, blo, idesc, 1u);
-                        mma_f16(acc, ahi, bhi, idesc, ks ? 1u : 0u);
+                        mma_f16(acc, ahi, bhi, idesc, k4 ? 1u : 0u);
                     }
                     mma_commit(b_free(buf));
                     mma_commit(acc_full(buf));
-                    PTC_TRACE_B(0, ti, 2);
+                    if (hh == 0) PTC_TRACE_B(0, ti, 2);
                 }
             }
         } else if (warp <= CW) {
@@ -901,13 +913,16 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                 const size_t xoff = (((dch + ac) * 2 + (s & 1)) * RT + r) * (size_t)(NC * ELS) + KSL * q + 32 * q4 + lane;
 #pragma unroll
                 for (int c0 = 0; c0 < NC; c0 += 16) {
-                    uint32_t mn[16], cx[16];
-                    tmem_ld16(lane_base + (uint32_t)(buf * 128 + c0), mn);
-                    tmem_ld16(lane_base + (uint32_t)(buf * 128 + 64 + c0), cx);
+                    uint32_t mn[16], cx[16], mn1[16], cx1[16];
+                    tmem_ld16(lane_base + (uint32_t)(buf * 256 + c0), mn);
+                    tmem_ld16(lane_base + (uint32_t)(buf * 256 + 64 + c0), cx);
+                    tmem_ld16(lane_base + (uint32_t)(buf * 256 + 128 + c0), mn1);
+                    tmem_ld16(lane_base + (uint32_t)(buf * 256 + 192 + c0), cx1);
                     tmem_ld_wait();
 #pragma unroll
                     for (int c = 0; c < 16; ++c) {
-                        const float v = (__uint_as_float(mn[c]) + __uint_as_float(cx[c]) * LO_UNSCALE) * invS;
+                        const float v = ((__uint_as_float(mn[c]) + __uint_as_float(mn1[c])) +
+                                         (__uint_as_float(cx[c]) + __uint_as_float(cx1[c])) * LO_UNSCALE) * invS;
                         // one chunk per group: self-validating words {step tag : float}, no release fence, no counters
                         if (LL) st_tagged(reinterpret_cast<u64 *>(a.xe) + xoff + (size_t)(c0 + c) * ELS, a.tag_base + (unsigned)s, __float_as_uint(v));
                         else a.xe[xoff + (size_t)(c0 + c) * ELS] = v;
@@ -1030,7 +1045,7 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
     __syncthreads();
     if (give_up_s && tid == 0) atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT);
     cluster_sync_all();
-    if (warp == 0) tmem_dealloc(tmem, 256);
+    if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 // =====================================================================================================
