@@ -37,6 +37,8 @@ sys.path.insert(0, os.path.join(ROOT, "project-currennt-public_b200"))
 TRAFFIC_BYTES_PER_CELL_STEP = {
     ("cfg1", "lstm_fwd_recurrence", "persistent_ffma"): 26.1,
     ("cfg1", "lstm_bwd_recurrence", "persistent_ffma"): 32.2,
+    ("cfg4", "lstm_fwd_recurrence", "persistent_tensor_core"): 32.3,
+    ("cfg4", "lstm_bwd_recurrence", "persistent_tensor_core"): 37.2,
 }
 
 METRIC = "blstm_train_step_frames_per_sec"
