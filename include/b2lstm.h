@@ -53,8 +53,8 @@ const char *b2_version(void);
  * C(m x n) = op(A) op(B) (+ C if accumulate), all column-major device pointers with leading
  * dimensions lda/ldb/ldc; op = transpose when the flag is non-zero.  The reference rejects
  * (transA && transB) (Matrix.cu:259-260); so does this call (B2_ERR_BAD_ARG).
- * Runs on tensor cores (3xTF32, fp32 accumulate) when the shape qualifies, otherwise as an
- * FFMA kernel; `force_ffma` non-zero always selects the latter.
+ * Runs on tensor cores when the shape qualifies (operands split into scaled fp16 high and low parts,
+ * three products, fp32 accumulation: the accuracy of an fp32 GEMM), otherwise as an FFMA kernel; `force_ffma` non-zero always selects the latter.
  * ------------------------------------------------------------------------------------------ */
 int b2_matrix_multiply(float *C, int ldc, const float *A, int lda, int transA, const float *B, int ldb,
                        int transB, int m, int n, int k, int accumulate, int force_ffma, b2_stream stream);

@@ -65,9 +65,16 @@ int gemm_ffma(float *C, long ldc, const float *A, long sam, long sak, const floa
 // Tensor-core path (gemm_tc.cu): operands are first split into tf32 hi/lo parts, stored densely as
 // [outer][ld] with the contiguous index padded to a multiple of 4 floats.
 struct SplitOperand {
-    const float *hi, *lo;
-    long ld;
-    bool kmajor;   // true: the contraction index k is the contiguous one; false: m (resp. n) is
+    const float *hi, *lo;   // the two parts; they hold halves when f16 is set
+    long ld;                // elements between consecutive rows
+    bool kmajor;            // true: the contraction index k is the contiguous one; false: m (resp. n) is
+    bool f16 = false;       // fp16 parts with a power-of-two scale (tf32 parts otherwise)
+    const unsigned *maxbits = nullptr;   // f16: device word with the bit pattern of the operand's largest finite |x|
+    // shifts both parts by `elems` elements
+    void advance(size_t elems) {
+        if (f16) { hi = (const float *)((const unsigned short *)hi + elems); lo = (const float *)((const unsigned short *)lo + elems); }
+        else { hi += elems; lo += elems; }
+    }
 };
 // bump arena for the hi/lo copies; grows by reallocation (which waits for the device)
 struct TcScratch {
@@ -77,10 +84,12 @@ struct TcScratch {
     float *take(size_t floats);
     void release();
 };
-size_t split_floats(int outer, int inner);
+size_t split_floats(int outer, int inner, bool f16 = true);
 int split_tf32(const float *src, long s_outer, int outer, int inner, float *hi, float *lo, long ldp, cudaStream_t st);
+int split_f16(const float *src, long s_outer, int outer, int inner, void *hi, void *lo, long ldp, unsigned *maxbits,
+              cudaStream_t st);
 int split_operand(TcScratch &sc, const float *src, long s_outer, int outer, int inner, bool kmajor, SplitOperand *out,
-                  cudaStream_t st);
+                  cudaStream_t st, bool f16 = true);
 bool gemm_tc_supported(const SplitOperand &A, const SplitOperand &B, int m, int n, int k);
 int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, int m, int n, int k, bool accumulate,
             float *ws, size_t ws_floats, int *status, cudaStream_t st);

@@ -31,18 +31,35 @@ float *TcScratch::take(size_t floats) {
 // split a strided matrix view whose contiguous index has `inner` entries and whose other index has
 // `outer` entries `s_outer` floats apart; returns the dense operand description
 int split_operand(TcScratch &sc, const float *src, long s_outer, int outer, int inner, bool kmajor, SplitOperand *out,
-                  cudaStream_t st) {
-    const long ldp = (inner + 3) & ~3L;
-    float *hi = sc.take((size_t)outer * ldp), *lo = sc.take((size_t)outer * ldp);
-    if (!hi || !lo) { set_error("split_operand: operand arena exhausted"); return B2_ERR_BAD_SHAPE; }
-    B2_TRY(split_tf32(src, s_outer, outer, inner, hi, lo, ldp, st));
+                  cudaStream_t st, bool f16) {
+    if (!f16) {
+        const long ldp = (inner + 3) & ~3L;
+        float *hi = sc.take((size_t)outer * ldp), *lo = sc.take((size_t)outer * ldp);
+        if (!hi || !lo) { set_error("split_operand: operand arena exhausted"); return B2_ERR_BAD_SHAPE; }
+        B2_TRY(split_tf32(src, s_outer, outer, inner, hi, lo, ldp, st));
+        *out = SplitOperand{};
+        out->hi = hi; out->lo = lo; out->ld = ldp; out->kmajor = kmajor;
+        return B2_OK;
+    }
+    // fp16 parts: rows padded to 8 halves (16 bytes, what a tensor map wants of a row pitch)
+    const long ldp = (inner + 7) & ~7L;
+    const size_t part = ((size_t)outer * ldp + 1) / 2;   // floats that hold one part
+    float *hi = sc.take(part), *lo = sc.take(part), *mx = sc.take(1);
+    if (!hi || !lo || !mx) { set_error("split_operand: operand arena exhausted"); return B2_ERR_BAD_SHAPE; }
+    B2_TRY(split_f16(src, s_outer, outer, inner, hi, lo, ldp, (unsigned *)mx, st));
     out->hi = hi; out->lo = lo; out->ld = ldp; out->kmajor = kmajor;
+    out->f16 = true; out->maxbits = (const unsigned *)mx;
     return B2_OK;
 }
 
-size_t split_floats(int outer, int inner) {
-    const size_t ldp = (size_t)((inner + 3) & ~3);
-    return 2 * (((size_t)outer * ldp + 63) & ~(size_t)63);
+size_t split_floats(int outer, int inner, bool f16) {
+    if (!f16) {
+        const size_t ldp = (size_t)((inner + 3) & ~3);
+        return 2 * (((size_t)outer * ldp + 63) & ~(size_t)63);
+    }
+    const size_t ldp = (size_t)((inner + 7) & ~7);
+    const size_t part = ((size_t)outer * ldp + 1) / 2;
+    return 2 * ((part + 63) & ~(size_t)63) + 64;
 }
 
 bool gemm_wants_tc(long sam, long sak, long sbk, long sbn, int m, int n, int k) {

@@ -186,12 +186,13 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
     const bool tc = !force_ffma && scratch && gemm_wants_tc(1, pls, 4 * ls, 1, pls, 4 * ls, N);
     SplitOperand sD{}, sX{}, sY{}, sW{};
     if (tc) {
-        // every operand of the four contractions is split into tf32 hi/lo parts ONCE and reused:
+        // every operand of the four contractions is split into hi/lo parts ONCE and reused:
         // deltas feed dX, dW_in and dW_rec; the layouts [frame][unit] serve both as K-major and
         // as MN-major operands, only the role of the contiguous index changes
         Phase ph(*this, "lstm_split_tf32");
-        B2_TRY(scratch->reserve(split_floats(N, 4 * ls) + split_floats(N, pls) + split_floats(N, ls) +
-                                split_floats(4 * ls, pls)));
+        const bool f16 = !tcrec_used;   // the per-timestep tensor-core recurrence leaves tf32 parts: its partners follow
+        B2_TRY(scratch->reserve(split_floats(N, 4 * ls, f16) + split_floats(N, pls, f16) + split_floats(N, ls, f16) +
+                                split_floats(4 * ls, pls, f16)));
         scratch->used = 0;
         if (tcrec_used) {
             // the tensor-core recurrence has already written the hi/lo parts of the deltas and of y
@@ -201,8 +202,8 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
             B2_TRY(split_operand(*scratch, bufs.deltas, 4 * ls, N, 4 * ls, true, &sD, st));
             B2_TRY(split_operand(*scratch, y, ls, N, ls, false, &sY, st));
         }
-        B2_TRY(split_operand(*scratch, x, pls, N, pls, false, &sX, st));
-        B2_TRY(split_operand(*scratch, w, pls, 4 * ls, pls, false, &sW, st));
+        B2_TRY(split_operand(*scratch, x, pls, N, pls, false, &sX, st, f16));
+        B2_TRY(split_operand(*scratch, w, pls, 4 * ls, pls, false, &sW, st, f16));
     }
     // error to the preceding layer (reference: 4*D Sgemm, LstmLayer.cu:2298-2334): dX = W_in * deltas
     if (dx) {
@@ -243,7 +244,7 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
             double best = 0.0;
             for (int sp = 1; sp <= 64 && (size_t)sp * 4 * D * per <= ws_floats && (long)sp * 256 <= K; ++sp) {
                 const int waves = (tiles * sp + sms - 1) / sms;
-                const double t = waves * (0.4 * ((K + sp - 1) / sp) / 32.0 + 3.0) + (double)sp * 4 * D * per * 8.0 / 5.0e6;
+                const double t = waves * (0.4 * ((K + sp - 1) / sp) / 64.0 + 3.0) + (double)sp * 4 * D * per * 8.0 / 5.0e6;
                 if (!splits || t < best) { best = t; splits = sp; }
             }
             if (splits >= 1) {
@@ -275,8 +276,8 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
                     SplitOperand A = sY, B = sD;
                     const size_t ao = (size_t)d * els + (d ? (size_t)P * sY.ld : 0);
                     const size_t bo = (size_t)g * ls + (size_t)d * els + (d ? 0 : (size_t)P * sD.ld);
-                    A.hi += ao; A.lo += ao; A.kmajor = false;
-                    B.hi += bo; B.lo += bo; B.kmajor = false;
+                    A.advance(ao); A.kmajor = false;
+                    B.advance(bo); B.kmajor = false;
                     B2_TRY(gemm_tc(C, els, A, B, els, els, K, false, ws, ws_floats, status_dev, st));
                 } else {
                     const float *A = y + (size_t)d * els + (d ? (size_t)P * ls : 0);

@@ -70,7 +70,7 @@ constexpr uint32_t A_HALF = 32768, A_BYTES = 65536;   // weight image: hi, lo of
 __host__ __device__ constexpr int fwd_cell_warps(bool ll) { return ll ? 8 : 16; }
 __host__ __device__ constexpr int bwd_cell_warps(bool ll) { return ll ? 4 : 8; }
 __host__ __device__ constexpr int fwd_threads(bool ll) { return 32 * (8 + fwd_cell_warps(ll)); }
-__host__ __device__ constexpr int bwd_threads(bool ll) { return 32 * (11 + bwd_cell_warps(ll)); }
+__host__ __device__ constexpr int bwd_threads(bool ll) { return 32 * (12 + bwd_cell_warps(ll)); }
 
 // Optional timing trace (build with -DB2_PTC_TRACE): block 0 records clock64() at the hand-over points of its
 // roles for the first chunk-steps of a launch; b2_debug_ptc_trace copies the records out.
@@ -168,8 +168,8 @@ struct Geo {
     static constexpr uint32_t F_B = A_BYTES, F_ZOWN = F_B + 2 * B_BUF, F_ZRECV = F_ZOWN + 2 * ZBLK;
     static constexpr uint32_t F_END = F_ZRECV + 2 * (KS - 1) * ZBLK;
     // backward
-    static constexpr uint32_t B_B = A_BYTES, B_ESUM = B_B + 2 * B_BUF, B_DSTAGE = B_ESUM + 2 * NC * UPC * 4;
-    static constexpr uint32_t B_END = B_DSTAGE + 2 * NC * 4 * UPC * 2;
+    static constexpr uint32_t B_B = A_BYTES, B_ESUM = B_B + 2 * B_BUF;
+    static constexpr uint32_t B_END = B_ESUM + 2 * NC * UPC * 4;
     static constexpr size_t fwd_smem() { return F_END + 1024; }
     static constexpr size_t bwd_smem() { return B_END + 1024; }
 };
@@ -639,7 +639,7 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
     constexpr int RT = G::RT, CPT = NC / (4 * CW);   // a cell warp covers 8 units x 4 sequences
     static_assert(CPT >= 1, "more cell warps than cells");
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) u64 bars[16];
+    __shared__ __align__(8) u64 bars[18];
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int give_up_s;
     __shared__ int lens_s[MAXC * NC], Tc_s[MAXC], Tmax_s;
@@ -656,6 +656,7 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
     auto acc_free = [&](int b) { return bar0 + 8u * (uint32_t)(6 + b); };  // drain -> MMA
     auto e_full = [&](int b) { return bar0 + 8u * (uint32_t)(8 + b); };    // reduce warps -> cell warps
     auto e_free = [&](int b) { return bar0 + 8u * (uint32_t)(10 + b); };   // cell warps -> reduce warps
+    auto s_full = [&](int b) { return bar0 + 8u * (uint32_t)(16 + b); };   // cell warps have written the block's share of operand B -> sender
 
     const int P = a.sh.P, T = a.sh.T, ls = a.sh.ls, D = a.sh.D;
     const int grp = blockIdx.x / G::GROUP, ngroups = gridDim.x / G::GROUP;
@@ -669,6 +670,7 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
             mbar_init(acc_full(b), 2); mbar_init(acc_free(b), 4);
             mbar_init(e_full(b), 4); mbar_init(e_free(b), CW);
             mbar_init(rel_full(b), 4); mbar_init(rel_free(b), 1);
+            mbar_init(s_full(b), CW);
         }
         give_up_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -682,7 +684,7 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
 
     // producer side (cell -> MMA -> drain) counts the chunk-steps whose deltas somebody consumes (s + 1 < Tc);
     // consumer side (reduce -> cell) counts the chunk-steps that receive a recurrent error (s >= 1)
-    int mp_m = 0, mp_c = 0, mp_d = 0, mc_r = 0, mc_c = 0, mp_p = 0;
+    int mp_m = 0, mp_c = 0, mp_d = 0, mc_r = 0, mc_c = 0, mp_p = 0, mp_s = 0;
     const int nwork = D * a.nslices;
     for (int wi = grp; wi < nwork; wi += ngroups) {
         const int d = wi % D, sl = wi / D;
@@ -718,13 +720,16 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                     tc_fence_after();
                     const uint32_t acc = tmem + (uint32_t)(buf * 256 + hh * 128);
                     const uint32_t bb = sbase + G::B_B + (uint32_t)buf * G::B_BUF;
+                    // Operand B (the row tile's gate deltas) is stored WITHOUT swizzle: for every 16-byte chunk along the
+                    // contraction (8 gate rows = the 8 units of one block and gate) the core matrices of all sequences
+                    // are contiguous, so that a block hands its share to a peer with one bulk copy per gate.
 #pragma unroll
                     for (int k4 = 0; k4 < 4; ++k4) {
                         const int ks = 4 * hh + k4;
                         const uint32_t ao = (uint32_t)(ks >> 2) * 16384u + (uint32_t)(ks & 3) * 32u;
-                        const uint32_t bo = (uint32_t)(ks >> 2) * (NC * 128u) + (uint32_t)(ks & 3) * 32u;
+                        const uint32_t bo = (uint32_t)ks * 2u * (NC * 16u);
                         const u64 ahi = desc_kmajor_sw128(sbase + ao, 1024), alo = desc_kmajor_sw128(sbase + A_HALF + ao, 1024);
-                        const u64 bhi = desc_kmajor_sw128(bb + bo, 1024), blo = desc_kmajor_sw128(bb + G::B_HL + bo, 1024);
+                        const u64 bhi = desc_kmajor_nosw(bb + bo, NC * 16u, 128), blo = desc_kmajor_nosw(bb + G::B_HL + bo, NC * 16u, 128);
                         mma_f16(acc + 64u, alo, bhi, idesc, k4 ? 1u : 0u);
                         mma_f16(acc + 64u, ahi, blo, idesc, 1u);
                         mma_f16(acc, ahi, bhi, idesc, k4 ? 1u : 0u);
@@ -743,7 +748,6 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
             const float p_ig = __ldg(a.w + off.peep + u), p_fg = __ldg(a.w + off.peep + (size_t)ls + u);
             const float p_og = __ldg(a.w + off.peep + 2 * (size_t)ls + u);
             const float *esum = reinterpret_cast<const float *>(gbase + G::B_ESUM);
-            unsigned short *dstage = reinterpret_cast<unsigned short *>(gbase + G::B_DSTAGE);   // [hi/lo][n][gate*8 + jj]
 
             // everything a step reads besides the recurrent error is fetched when the previous chunk-step is done
             float f_dy[CPT], f_act[CPT][4], f_c[CPT], f_cp[CPT], f_nfg[CPT], f_nce[CPT], f_ndig[CPT], f_ndfg[CPT];
@@ -820,6 +824,8 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                 if (bar_named_or(1, CT, !ok)) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
                 if (et == 0) PTC_TRACE_B(1, ti, 2);
                 float *ce_cur = a.bf.cerr + (size_t)(s & 1) * P * ls;
+                const uint32_t bb_w = sbase + G::B_B + (uint32_t)pbuf * G::B_BUF;
+                float dl_r[CPT][4], ce_r[CPT];
 #pragma unroll
                 for (int i = 0; i < CPT; ++i) {
                     const int n = slot * CPT + i, pg = p0 + n;
@@ -837,43 +843,38 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                         dni = limited_error(dni); dig = limited_error(dig); dfg = limited_error(dfg); dog = limited_error(dog);
                     }
                     if (feeds) {
+                        // this cell's four deltas as fp16 hi / lo, straight into this block's operand buffer: element
+                        // (sequence n, gate row g*32 + q*8 + jj) lives in chunk g*4 + q, row n of its core matrix
                         const float dl[4] = {dni, dig, dfg, dog};
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
                             const unsigned x = split_f16(dl[g]);
-                            dstage[n * (4 * UPC) + g * UPC + jj] = (unsigned short)(x & 0xffffu);
-                            dstage[(NC + n) * (4 * UPC) + g * UPC + jj] = (unsigned short)(x >> 16);
+                            const uint32_t o = (uint32_t)(g * 4 + q) * (NC * 16u) + (uint32_t)(n >> 3) * 128u + (uint32_t)(n & 7) * 16u + (uint32_t)jj * 2u;
+                            asm volatile("st.shared.b16 [%0], %1;" ::"r"(bb_w + o), "h"((unsigned short)(x & 0xffffu)) : "memory");
+                            asm volatile("st.shared.b16 [%0], %1;" ::"r"(bb_w + G::B_HL + o), "h"((unsigned short)(x >> 16)) : "memory");
                         }
                     }
-                    if (pg < P) {
-                        const size_t o = ((size_t)t * P + pg) * 4 * ls + u;
-                        a.bf.deltas[o] = dni; a.bf.deltas[o + ls] = dig; a.bf.deltas[o + 2 * (size_t)ls] = dfg; a.bf.deltas[o + 3 * (size_t)ls] = dog;
-                        ce_cur[(size_t)pg * ls + u] = ce;
-                    }
+                    dl_r[i][0] = dni; dl_r[i][1] = dig; dl_r[i][2] = dfg; dl_r[i][3] = dog; ce_r[i] = ce;
                 }
                 if (et == 0) PTC_TRACE_B(1, ti, 3);
                 if (feeds) {
-                    bar_named(1, CT);
-                    // 16-byte operand chunks (the 8 units of one gate and sequence) into this block's operand B and the peers'
-                    const uint32_t bb = sbase + G::B_B + (uint32_t)pbuf * G::B_BUF;
-                    constexpr int NCHUNK = 2 * NC * 4;
-                    for (int ci = et; ci < NCHUNK; ci += CT) {
-                        const int g = ci & 3, n = (ci >> 2) % NC, hl = ci / (4 * NC);
-                        const uint4 v = *reinterpret_cast<const uint4 *>(dstage + (hl * NC + n) * (4 * UPC) + g * UPC);
-                        const int clc = g * 4 + q;   // chunk index along the 128 gate rows of the row tile
-                        const uint32_t o = (uint32_t)hl * G::B_HL + (uint32_t)(clc >> 3) * (NC * 128u) + (uint32_t)n * 128u +
-                                           (uint32_t)(((clc & 7) ^ (n & 7)) * 16);
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(bb + o), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-#pragma unroll
-                        for (int pr = 0; pr < KS; ++pr)
-                            if (pr != q) st_async_v4(map_to_rank(bb + o, (uint32_t)pr), v.x, v.y, v.z, v.w, map_to_rank(b_full(pbuf), (uint32_t)pr));
-                    }
+                    // this warp's share of the operand is in place: visible to the async proxy, then over to the sender warp
                     fence_async_smem();
-                    bar_named(1, CT);
-                    // one arrival per phase; it also announces the bytes the peers deliver into this buffer
-                    if (et == 0) mbar_expect_tx(b_full(pbuf), (uint32_t)(KS - 1) * 2u * NC * 4u * UPC * 2u);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(s_full(pbuf));
                 }
                 if (et == 0) PTC_TRACE_B(1, ti, 4);
+                // the layer's own copies go out after the hand-over (the proxy fence above would wait for them)
+#pragma unroll
+                for (int i = 0; i < CPT; ++i) {
+                    const int pg = p0 + slot * CPT + i;
+                    if (pg < P) {
+                        const size_t o = ((size_t)t * P + pg) * 4 * ls + u;
+                        a.bf.deltas[o] = dl_r[i][0]; a.bf.deltas[o + ls] = dl_r[i][1];
+                        a.bf.deltas[o + 2 * (size_t)ls] = dl_r[i][2]; a.bf.deltas[o + 3 * (size_t)ls] = dl_r[i][3];
+                        ce_cur[(size_t)pg * ls + u] = ce_r[i];
+                    }
+                }
                 more = next_item(s, cl, ncl, Tc_s, Tmax);
                 if (more) fetch(s, cl);
                 if (et == 0) PTC_TRACE_B(1, ti, 5);
@@ -888,6 +889,29 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                         a.bf.deltas[o] = 0.0f; a.bf.deltas[o + ls] = 0.0f; a.bf.deltas[o + 2 * (size_t)ls] = 0.0f; a.bf.deltas[o + 3 * (size_t)ls] = 0.0f;
                     }
                 }
+            }
+        } else if (warp == CW + 11) {
+            // ------------------------------------ sender: the block's share of operand B to the three peers ------------------------------------
+            // One bulk copy per (hi/lo, gate, peer): NC x 16 contiguous bytes, counted on the peer's barrier.  Issuing such a
+            // copy holds its thread for a microsecond or so, which is why the cell warps do not do it themselves.
+            int s = 0, cl = -1;
+            while (next_item(s, cl, ncl, Tc_s, Tmax)) {
+                if (s + 1 >= Tc_s[cl]) continue;
+                if (give_up_s) break;
+                const int pbuf = mp_s & 1;
+                const uint32_t pph = (uint32_t)(mp_s >> 1) & 1u;
+                ++mp_s;
+                const bool ok = mbar_wait_bounded<false>(s_full(pbuf), pph, &give_up_s, WAIT_CYCLES);
+                if (!__all_sync(0xffffffffu, ok)) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
+                const uint32_t bb_w = sbase + G::B_B + (uint32_t)pbuf * G::B_BUF;
+                // one arrival per phase; it also announces the bytes the peers deliver into this buffer
+                if (lane == 0) mbar_expect_tx(b_full(pbuf), (uint32_t)(KS - 1) * 8u * NC * 16u);
+                if (lane < 8 * (KS - 1)) {
+                    const int pr = (q + 1 + lane / 8) & (KS - 1), hl = (lane >> 2) & 1, g = lane & 3;
+                    const uint32_t o = (uint32_t)hl * G::B_HL + (uint32_t)(g * 4 + q) * (NC * 16u);
+                    bulk_s2c(map_to_rank(bb_w + o, (uint32_t)pr), bb_w + o, NC * 16u, map_to_rank(b_full(pbuf), (uint32_t)pr));
+                }
+                __syncwarp();
             }
         } else if (warp <= CW + 4) {
             // ------------------------------------------------ drain: partial output errors to global memory ------------------------------------------------
@@ -1022,6 +1046,7 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                 // the 16 blocks (rs, qu) that hold partials for this block's units
                 ok = ok && poll_flags(a.flags + (dch + ac) * G::GROUP + qu, KS, a.tag_base + (unsigned)(s - 1), lane, &give_up_s, a.status);
                 if (!ok) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
+                if (rt == 0) PTC_TRACE_B(2, ti, 3);
                 if (active) {
                     const float *src = a.xe + (((dch + ac) * 2 + ((s - 1) & 1)) * RT) * (size_t)(NC * ELS) + (size_t)n * ELS + 32 * r + q * UPC + 4 * hf;
                     float4 v[RT];

@@ -110,6 +110,16 @@ __device__ __forceinline__ u64 desc_kmajor_sw128(uint32_t addr, uint32_t sbo_byt
     d |= 2ULL << 61;                                   // SWIZZLE_128B
     return d;
 }
+// The same for a K-major tile without swizzle: 8 rows x 16 bytes form a contiguous 128-byte core matrix; core matrices
+// that follow each other along K lie `lbo` bytes apart, 8-row groups `sbo` bytes apart.
+__device__ __forceinline__ u64 desc_kmajor_nosw(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    u64 d = 0;
+    d |= (u64)((addr >> 4) & 0x3FFF);
+    d |= (u64)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (u64)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= 1ULL << 46;
+    return d;
+}
 // instruction descriptor of kind::f16 with fp16 operands, both K-major, fp32 accumulation
 __device__ __forceinline__ uint32_t idesc_f16(int M, int N) {
     return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
@@ -151,6 +161,12 @@ __device__ __forceinline__ void fence_async_all() { asm volatile("fence.proxy.as
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                  "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// bulk copy from this block's shared memory into a cluster peer's (addresses from mapa); bytes counted on the peer's barrier
+__device__ __forceinline__ void bulk_s2c(uint32_t remote_dst, uint32_t src, uint32_t bytes, uint32_t remote_bar) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(remote_dst),
+                 "r"(src), "r"(bytes), "r"(remote_bar)
                  : "memory");
 }
 // step counters blocks publish to each other: release after the data, acquire before reading it

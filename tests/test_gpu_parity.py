@@ -374,7 +374,7 @@ def test_matrix_multiply_wrapper():
 
 def test_tensor_core_gemm_keeps_fp32_accuracy_on_long_contractions():
     """The weight-gradient products contract over all frames of a fraction (tens of thousands of
-    terms).  The 3xTF32 tensor-core kernel must stay as close to the float64 result as a plain fp32
+    terms).  The tensor-core kernel (fp16 high/low operand parts) must stay as close to the float64 result as a plain fp32
     FFMA kernel does: relative L2 error below 2e-6 and within a small factor of the FFMA error."""
     import torch
     import b2lstm
@@ -394,6 +394,42 @@ def test_tensor_core_gemm_keeps_fp32_accuracy_on_long_contractions():
             errs[ffma] = np.linalg.norm(got - want) / np.linalg.norm(want)
         print("gemm %dx%dx%d rel L2 error: ffma %.3g tensor %.3g" % (m, n, k, errs[1], errs[0]))
         assert errs[0] < 2e-6 and errs[0] < 8 * errs[1] + 2e-7, errs
+
+
+def test_tensor_core_gemm_over_operand_magnitudes_and_dynamic_range():
+    """The fp16 operand parts carry a power-of-two scale per operand, taken from its largest finite entry.  Products of
+    very small, very large and all-zero operands, and of operands whose entries span many orders of magnitude (the
+    deltas of a long sequence do), must stay at fp32 accuracy against float64: per row of the result, the error is
+    measured against the row's own scale sum_k |a_ik||b_kj|."""
+    import torch
+    import b2lstm
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(17)
+    m, n, k = 256, 320, 4096
+    base_a = rng.standard_normal((k, m))
+    base_b = rng.standard_normal((k, n))
+    # rows of A whose entries are 1e-6 .. 1 of the largest; the same over the contraction index for B
+    spread_a = base_a * (10.0 ** rng.uniform(-6, 0, size=(1, m)))
+    spread_b = base_b * (10.0 ** rng.uniform(-6, 0, size=(k, 1)))
+    cases = [("small", base_a * 1e-22, base_b * 1e-12), ("large", base_a * 1e15, base_b * 1e12),
+             ("mixed", base_a * 1e-20, base_b * 1e18), ("spread", spread_a, spread_b),
+             ("zero", base_a * 0.0, base_b)]
+    for name, a64, b64 in cases:
+        A, B = a64.astype(np.float32), b64.astype(np.float32)
+        want = A.T.astype(np.float64) @ B.astype(np.float64)
+        mag = np.abs(A.T.astype(np.float64)) @ np.abs(B.astype(np.float64))
+        tA, tB = torch.from_numpy(A).to(dev), torch.from_numpy(B).to(dev)
+        tC = torch.full((n, m), 7.0, device=dev)
+        b2lstm.matrix_multiply(tC, m, tA, m, 0, tB, n, 1, m, n, k, accumulate=False, force_ffma=0)
+        torch.cuda.synchronize()
+        got = tC.cpu().numpy().T.astype(np.float64)
+        assert np.isfinite(got).all(), name
+        if name == "zero":
+            assert (got == 0.0).all()
+            continue
+        rel = np.abs(got - want) / mag
+        print("gemm operands %-6s: largest error / sum|a||b| = %.3g" % (name, rel.max()))
+        assert rel.max() < 3e-7, (name, rel.max())
 
 
 def test_padding_that_does_not_trail_its_sequence_is_refused_when_the_check_is_on():
