@@ -107,6 +107,21 @@ struct PtcArgs {
     int nchunks;           // chunks of NC sequences in all
 };
 
+// The activations of the cell warps.  They are the longest stretch of instructions in a chunk-step, so they use the
+// hardware approximations: ex2.approx on x * log2(e) (__expf: 2 + |1.17 x| ulp on e^-x, which the logistic function damps by
+// y (1 - y) <= 1/4) and rcp.approx (1 ulp).  The result stays within 2 ulp of the correctly rounded logistic function,
+// the same class as expf + IEEE division; the clamps are those of the reference's safeExp
+// (helpers/NumericLimits / activation functions: exp arguments limited to +-88.72).
+__device__ __forceinline__ float fast_logistic(float x) {
+    const float lim = 88.722839f;
+    if (x < lim) {
+        if (x > -lim) return __fdividef(1.0f, 1.0f + __expf(-x));
+        return 0.0f;
+    }
+    return 1.0f;
+}
+__device__ __forceinline__ float fast_tanh(float x) { return 2.0f * fast_logistic(2.0f * x) - 1.0f; }
+
 __device__ __forceinline__ unsigned split_f16(float x) {   // hi in the low half, lo in the high half
     const __half h = __float2half_rn(x);
     const __half l = __float2half_rn((x - __half2float(h)) * LO_SCALE);
@@ -339,12 +354,17 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                 if (give_up_s) break;
                 const int pb = m_p & 1;
                 const uint32_t pph = (uint32_t)(m_p >> 1) & 1u;
+                const int ti = m_p;
+                (void)ti;
                 ++m_p;
+                if (lane == 0) PTC_TRACE(2, ti, 4);
                 const bool ok = mbar_wait_bounded<false>(rel_full(pb), pph, &give_up_s, WAIT_CYCLES);
                 if (!__all_sync(0xffffffffu, ok)) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
                 if (lane == 0) {
+                    PTC_TRACE(2, ti, 5);
                     st_release_u32(a.flags + (dch + (size_t)(sl + cl * a.nslices)) * G::GROUP + bidx, a.tag_base + (unsigned)s);
                     mbar_arrive(rel_free(pb));
+                    PTC_TRACE(2, ti, 6);
                 }
                 __syncwarp();
             }
@@ -419,24 +439,28 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
             const uint32_t img_cb = (uint32_t)((r & 3) >> 1) * (NC * 128u);            // column block
             const int img_kc = 4 * (r & 1) + q;                                        // 16-byte chunk inside the 128-byte row
 
-            float pre[CPT][4], cpv[CPT];
-            auto fetch = [&](int s2, int cl2) {
+            // Inputs of a chunk-step besides the recurrent sums: the projected inputs and the previous cell state.  With
+            // several chunks per group they are requested one whole chunk-step ahead (second register set), so that
+            // the loads have landed when the sums arrive; with one chunk the previous state is the one just computed.
+            float pre[CPT][4], cpv[CPT], pre_n[LL ? 1 : CPT][4], cpv_n[LL ? 1 : CPT];
+            auto fetch_into = [&](float (*pr)[4], float *cv, int s2, int cl2) {
                 const int t = d ? Tc_s[cl2] - 1 - s2 : s2, prev = d ? t + 1 : t - 1;
                 const int p0 = (sl + cl2 * a.nslices) * NC;
 #pragma unroll
                 for (int i = 0; i < CPT; ++i) {
                     const int n = slot * CPT + i, pg = p0 + n;
-                    cpv[i] = 0.0f;
+                    cv[i] = 0.0f;
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) pre[i][g] = 0.0f;
+                    for (int g = 0; g < 4; ++g) pr[i][g] = 0.0f;
                     if (pg < P && t < lens_s[cl2 * NC + n]) {
                         const float *ap = a.bf.acts + ((size_t)t * P + pg) * 4 * ls + u;
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) pre[i][g] = ap[(size_t)g * ls];
-                        if (s2 > 0) cpv[i] = a.bf.cells[((size_t)prev * P + pg) * ls + u];
+                        for (int g = 0; g < 4; ++g) pr[i][g] = ap[(size_t)g * ls];
+                        if (s2 > 0) cv[i] = a.bf.cells[((size_t)prev * P + pg) * ls + u];
                     }
                 }
             };
+            auto fetch = [&](int s2, int cl2) { fetch_into(pre, cpv, s2, cl2); };
             // One chunk per group: nothing overlaps, the step is a chain of latencies.  h[t] then travels as self-validating
             // words {step tag : hi16 : lo16} that these warps collect into operand B themselves, right after they have
             // published their own part: no release fence at the producers, no counter round trip, no bulk-copy start-up.
@@ -504,6 +528,12 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                 if (give_up_s) break;
                 const int ac = sl + cl * a.nslices, p0 = ac * NC;
                 const int t = d ? Tc_s[cl] - 1 - s : s;
+                int s_n = s, cl_n = cl;
+                bool more_n = false;
+                if constexpr (!LL) {
+                    more_n = next_item(s_n, cl_n, ncl, Tc_s, Tmax);
+                    if (more_n) fetch_into(pre_n, cpv_n, s_n, cl_n);
+                }
                 float z[CPT][4];
 #pragma unroll
                 for (int i = 0; i < CPT; ++i)
@@ -550,12 +580,12 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                         float x2 = pre[i][2] + z[i][2] + b4[2], x3 = pre[i][3] + z[i][3] + b4[3];
                         const float cp = cpv[i];
                         if (!first) { x1 += cp * pw[0]; x2 += cp * pw[1]; }
-                        ni[i] = act_tanh(x0); ig[i] = act_logistic(x1); fg[i] = act_logistic(x2);
+                        ni[i] = fast_tanh(x0); ig[i] = fast_logistic(x1); fg[i] = fast_logistic(x2);
                         float c = ni[i] * ig[i];
                         if (!first) c += cp * fg[i];
-                        og[i] = act_logistic(x3 + c * pw[2]);
+                        og[i] = fast_logistic(x3 + c * pw[2]);
                         cs[i] = c;
-                        hh[i] = act_tanh(c) * og[i];
+                        hh[i] = fast_tanh(c) * og[i];
                     }
                     if (publish && LL) {
                         st_tagged(reinterpret_cast<u64 *>(a.xh) + ((dch + ac) * 2 + (s & 1)) * (size_t)(NC * ELS) + (size_t)n * ELS + j,
@@ -576,6 +606,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                         }
                     }
                 }
+                if (ct == 0 && s > 0) PTC_TRACE(1, ti, 6);
                 if (publish && !LL) {
                     // this warp's part of h[t] is on its way: hand it to the publisher; the layer's own state is stored afterwards
                     const int pb = m_p & 1;
@@ -605,8 +636,20 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                         a.y[f * ls + u] = hh[i];
                     }
                 }
-                more = next_item(s, cl, ncl, Tc_s, Tmax);
-                if (more) fetch(s, cl);
+                if (ct == 0 && s > 0) PTC_TRACE(1, ti, 7);
+                if constexpr (LL) {
+                    more = next_item(s, cl, ncl, Tc_s, Tmax);
+                    if (more) fetch(s, cl);
+                } else {
+                    const bool same_chunk = (cl_n == cl);   // one chunk in this group: its previous cell state is cs[]
+                    s = s_n; cl = cl_n; more = more_n;
+#pragma unroll
+                    for (int i = 0; i < CPT; ++i) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) pre[i][g] = pre_n[i][g];
+                        cpv[i] = same_chunk ? cs[i] : cpv_n[i];
+                    }
+                }
                 if (ct == 0 && s > 1) PTC_TRACE(1, ti, 4);
             }
             // frames beyond a chunk's longest sequence are padding for all its sequences: outputs are zero there
@@ -833,7 +876,7 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                     if (pg < P && t < lens_s[cl * NC + n]) {
                         const float e = f_dy[i] + er[i];
                         const float ni = f_act[i][0], ig = f_act[i][1], fg = f_act[i][2], og = f_act[i][3];
-                        const float tc = act_tanh(f_c[i]);
+                        const float tc = fast_tanh(f_c[i]);
                         dog = d_logistic(og) * tc * e;
                         ce = og * d_tanh(tc) * e + p_og * dog;
                         if (!firstCall) ce += f_nfg[i] * f_nce[i] + p_ig * f_ndig[i] + p_fg * f_ndfg[i];
