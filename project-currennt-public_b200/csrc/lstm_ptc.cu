@@ -184,7 +184,10 @@ struct Geo {
     static constexpr uint32_t F_END = F_ZRECV + 2 * (KS - 1) * ZBLK;
     // backward
     static constexpr uint32_t B_B = A_BYTES, B_ESUM = B_B + 2 * B_BUF;
-    static constexpr uint32_t B_END = B_ESUM + 2 * NC * UPC * 4;
+    // what a cell hands to its own next step (forget gate, cell error, two gate deltas), for up to CARRY chunks per group
+    static constexpr int CARRY = 4;
+    static constexpr uint32_t B_CARRY = B_ESUM + 2 * NC * UPC * 4;
+    static constexpr uint32_t B_END = B_CARRY + CARRY * 4 * NC * UPC * 4;
     static constexpr size_t fwd_smem() { return F_END + 1024; }
     static constexpr size_t bwd_smem() { return B_END + 1024; }
 };
@@ -681,6 +684,8 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
     constexpr int CW = bwd_cell_warps(LL), BWD_THREADS = bwd_threads(LL), CT = 32 * CW;
     constexpr int RT = G::RT, CPT = NC / (4 * CW);   // a cell warp covers 8 units x 4 sequences
     static_assert(CPT >= 1, "more cell warps than cells");
+    // one chunk of 32 sequences per group: the cell warps send their part of operand B to the peers themselves (below)
+    constexpr bool SELF_SEND = LL && NC == 32;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) u64 bars[18];
     __shared__ uint32_t tmem_base_s;
@@ -709,7 +714,8 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
 
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
-            mbar_init(b_full(b), 1); mbar_init(b_free(b), KS + 1);   // two local MMA issuers + the other three blocks' drains
+            mbar_init(b_full(b), SELF_SEND ? CW : 1);   // every cell warp announces its part, or the sender warp does
+            mbar_init(b_free(b), KS + 1);        // two local MMA issuers + the other three blocks' drains
             mbar_init(acc_full(b), 2); mbar_init(acc_free(b), 4);
             mbar_init(e_full(b), 4); mbar_init(e_free(b), CW);
             mbar_init(rel_full(b), 4); mbar_init(rel_free(b), 1);
@@ -791,6 +797,10 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
             const float p_ig = __ldg(a.w + off.peep + u), p_fg = __ldg(a.w + off.peep + (size_t)ls + u);
             const float p_og = __ldg(a.w + off.peep + 2 * (size_t)ls + u);
             const float *esum = reinterpret_cast<const float *>(gbase + G::B_ESUM);
+            // A cell's forget-gate activation, cell error and input / forget gate deltas are read again by the same thread at the
+            // next step of the chunk: they stay in shared memory when the group has few enough chunks (else global memory).
+            float *carry_s = reinterpret_cast<float *>(gbase + G::B_CARRY);
+            const bool carry = (ncl <= G::CARRY) && !(LL && NC == 64);   // (one chunk of 64: measured slower, the kernel is out of registers)
 
             // everything a step reads besides the recurrent error is fetched when the previous chunk-step is done
             float f_dy[CPT], f_act[CPT][4], f_c[CPT], f_cp[CPT], f_nfg[CPT], f_nce[CPT], f_ndig[CPT], f_ndfg[CPT];
@@ -815,7 +825,10 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                         for (int g = 0; g < 4; ++g) f_act[i][g] = ap[(size_t)g * ls];
                         f_c[i] = a.bf.cells[f * ls + u];
                         if (!lastCall) f_cp[i] = a.bf.cells[((size_t)prevc * P + pg) * ls + u];
-                        if (s2 > 0) {
+                        if (s2 > 0 && carry) {
+                            const float *cr = carry_s + (size_t)(cl2 * 4) * (NC * UPC) + et * CPT + i;
+                            f_nfg[i] = cr[0]; f_nce[i] = cr[NC * UPC]; f_ndig[i] = cr[2 * NC * UPC]; f_ndfg[i] = cr[3 * NC * UPC];
+                        } else if (s2 > 0) {
                             const size_t fn = (size_t)next * P + pg;
                             f_nfg[i] = a.bf.acts[fn * 4 * ls + 2 * (size_t)ls + u];
                             f_nce[i] = ce_nxt[(size_t)pg * ls + u];
@@ -898,9 +911,37 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                         }
                     }
                     dl_r[i][0] = dni; dl_r[i][1] = dig; dl_r[i][2] = dfg; dl_r[i][3] = dog; ce_r[i] = ce;
+                    if (carry) {
+                        float *cr = carry_s + (size_t)(cl * 4) * (NC * UPC) + et * CPT + i;
+                        cr[0] = f_act[i][2]; cr[NC * UPC] = ce; cr[2 * NC * UPC] = dig; cr[3 * NC * UPC] = dfg;
+                    }
                 }
                 if (et == 0) PTC_TRACE_B(1, ti, 3);
-                if (feeds) {
+                if (feeds && SELF_SEND) {
+                    // One chunk per group: the step is a chain of latencies, and a bulk copy costs its issuer a microsecond.
+                    // Each warp sends the 16-byte pieces it has just written (its sequences, all gates, hi and lo) to the three
+                    // peers itself, with st.async counted on the peer's barrier, and announces its part of the local copy.
+                    fence_async_smem();
+                    __syncwarp();
+                    const int wq = et >> 5;                           // this cell warp covers sequences 4*CPT*wq .. +4*CPT
+#pragma unroll
+                    for (int i2 = 0; i2 < CPT; ++i2) {
+                        const int c = lane + 32 * i2, nl = c % (4 * CPT), gh = c / (4 * CPT);
+                        const int n = 4 * CPT * wq + nl, g = gh & 3, hl = gh >> 2;
+                        const uint32_t o = (uint32_t)hl * G::B_HL + (uint32_t)(g * 4 + q) * (NC * 16u) + (uint32_t)(n >> 3) * 128u + (uint32_t)(n & 7) * 16u;
+                        uint32_t v0, v1, v2, v3;
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(bb_w + o) : "memory");
+#pragma unroll
+                        for (int pr = 1; pr < KS; ++pr) {
+                            const uint32_t peer = (uint32_t)((q + pr) & (KS - 1));
+                            st_async_v4(map_to_rank(bb_w + o, peer), v0, v1, v2, v3, map_to_rank(b_full(pbuf), peer));
+                        }
+                    }
+                    if (lane == 0) {
+                        if (et == 0) mbar_expect_tx(b_full(pbuf), (uint32_t)(KS - 1) * 8u * NC * 16u);   // the bytes the peers deliver
+                        else mbar_arrive(b_full(pbuf));
+                    }
+                } else if (feeds) {
                     // this warp's share of the operand is in place: visible to the async proxy, then over to the sender warp
                     fence_async_smem();
                     __syncwarp();
@@ -915,7 +956,7 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
                         const size_t o = ((size_t)t * P + pg) * 4 * ls + u;
                         a.bf.deltas[o] = dl_r[i][0]; a.bf.deltas[o + ls] = dl_r[i][1];
                         a.bf.deltas[o + 2 * (size_t)ls] = dl_r[i][2]; a.bf.deltas[o + 3 * (size_t)ls] = dl_r[i][3];
-                        ce_cur[(size_t)pg * ls + u] = ce_r[i];
+                        if (!carry) ce_cur[(size_t)pg * ls + u] = ce_r[i];
                     }
                 }
                 more = next_item(s, cl, ncl, Tc_s, Tmax);
@@ -938,7 +979,7 @@ __global__ void __launch_bounds__(bwd_threads(LL), 1) lstm_bwd_ptc_kernel(PtcArg
             // One bulk copy per (hi/lo, gate, peer): NC x 16 contiguous bytes, counted on the peer's barrier.  Issuing such a
             // copy holds its thread for a microsecond or so, which is why the cell warps do not do it themselves.
             int s = 0, cl = -1;
-            while (next_item(s, cl, ncl, Tc_s, Tmax)) {
+            while (!SELF_SEND && next_item(s, cl, ncl, Tc_s, Tmax)) {
                 if (s + 1 >= Tc_s[cl]) continue;
                 if (give_up_s) break;
                 const int pbuf = mp_s & 1;
