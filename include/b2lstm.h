@@ -159,6 +159,14 @@ int b2_net_create(const char *network_json, int parallel_sequences, int max_seq_
  * every forget-gate bias of the (b)lstm layers that b2_net_create initialises at random from now on (layers whose
  * weights come from the JSON are left alone).  Process-wide, like the reference's Configuration; default 0. */
 void b2_config_set_lstm_forget_gate_bias(float value);
+
+/* Tuning of the persistent tensor-core recurrence (no counterpart in the reference).  The sequences of a fraction are
+ * processed in chunks; the chunks of a group of blocks are in flight together.  ll_chunks = the largest number of chunks
+ * per group that still uses the latency-optimised exchange (self-validating words through L2 instead of step counters
+ * and bulk copies); nc32_chunks = the largest number of chunks per group that are 32 sequences wide (wider fractions use
+ * chunks of 64).  The forward (backward = 0) and the backward sweep have settings of their own (defaults 1, 1 and 2, 2: the
+ * measured optimum on a B200).  Call before layers or networks are created. */
+void b2_config_set_ptc_plan(int backward, int ll_chunks, int nc32_chunks);
 void b2_net_destroy(b2_net *net);
 /* Layer::parallelSequences() / Layer::maxSeqLength() (layers/Layer.hpp:163-175) the net was created with */
 int b2_net_parallel_sequences(const b2_net *net);

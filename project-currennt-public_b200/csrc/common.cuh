@@ -86,10 +86,11 @@ struct TcScratch {
 };
 size_t split_floats(int outer, int inner, bool f16 = true);
 int split_tf32(const float *src, long s_outer, int outer, int inner, float *hi, float *lo, long ldp, cudaStream_t st);
+// bound > 0: the caller's promise that no |entry| exceeds it (saves the pass that finds the largest entry)
 int split_f16(const float *src, long s_outer, int outer, int inner, void *hi, void *lo, long ldp, unsigned *maxbits,
-              cudaStream_t st);
+              cudaStream_t st, float bound = 0.0f);
 int split_operand(TcScratch &sc, const float *src, long s_outer, int outer, int inner, bool kmajor, SplitOperand *out,
-                  cudaStream_t st, bool f16 = true);
+                  cudaStream_t st, bool f16 = true, float bound = 0.0f);
 bool gemm_tc_supported(const SplitOperand &A, const SplitOperand &B, int m, int n, int k);
 int gemm_tc(float *C, long ldc, const SplitOperand &A, const SplitOperand &B, int m, int n, int k, bool accumulate,
             float *ws, size_t ws_floats, int *status, cudaStream_t st);
@@ -190,6 +191,7 @@ struct PtcBuffers {
 };
 bool lstm_ptc_supported(const LstmShape &s);
 size_t lstm_ptc_image_bytes(int els, int D);
+void lstm_ptc_set_plan(bool backward, int ll_chunks, int nc32_chunks);
 void lstm_ptc_exchange_sizes(int els, int P, int D, size_t *xh_bytes, size_t *xe_floats, size_t *flag_words);
 int lstm_ptc_prepare(const LstmShape &s, const float *w, const PtcBuffers &pb, cudaStream_t st);
 int lstm_ptc_sweep(bool backward, const LstmShape &s, const LstmBuffers &b, const PtcBuffers &pb, const float *w, float *y,

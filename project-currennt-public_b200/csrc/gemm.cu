@@ -31,7 +31,7 @@ float *TcScratch::take(size_t floats) {
 // split a strided matrix view whose contiguous index has `inner` entries and whose other index has
 // `outer` entries `s_outer` floats apart; returns the dense operand description
 int split_operand(TcScratch &sc, const float *src, long s_outer, int outer, int inner, bool kmajor, SplitOperand *out,
-                  cudaStream_t st, bool f16) {
+                  cudaStream_t st, bool f16, float bound) {
     if (!f16) {
         const long ldp = (inner + 3) & ~3L;
         float *hi = sc.take((size_t)outer * ldp), *lo = sc.take((size_t)outer * ldp);
@@ -46,7 +46,7 @@ int split_operand(TcScratch &sc, const float *src, long s_outer, int outer, int 
     const size_t part = ((size_t)outer * ldp + 1) / 2;   // floats that hold one part
     float *hi = sc.take(part), *lo = sc.take(part), *mx = sc.take(1);
     if (!hi || !lo || !mx) { set_error("split_operand: operand arena exhausted"); return B2_ERR_BAD_SHAPE; }
-    B2_TRY(split_f16(src, s_outer, outer, inner, hi, lo, ldp, (unsigned *)mx, st));
+    B2_TRY(split_f16(src, s_outer, outer, inner, hi, lo, ldp, (unsigned *)mx, st, bound));
     out->hi = hi; out->lo = lo; out->ld = ldp; out->kmajor = kmajor;
     out->f16 = true; out->maxbits = (const unsigned *)mx;
     return B2_OK;

@@ -32,6 +32,7 @@
 #include <cuda.h>
 
 #include <cuda_fp16.h>
+#include <cstring>
 #include "common.cuh"
 
 namespace b2 {
@@ -546,6 +547,8 @@ __global__ void __launch_bounds__(256) absmax_kernel(const float *__restrict__ s
         if (m) atomicMax(maxbits, m);
     }
 }
+__global__ void set_word_kernel(unsigned *dst, unsigned v) { *dst = v; }
+inline unsigned __float_as_uint_host(float f) { unsigned u; memcpy(&u, &f, sizeof u); return u; }
 // x*S = hi + lo * 2^-11; both parts as fp16 bit patterns
 __device__ __forceinline__ void split_f16_one(float x, float S, unsigned short &h, unsigned short &l) {
     const float xs = x * S;
@@ -679,12 +682,17 @@ int split_tf32(const float *src, long s_outer, int outer, int inner, float *hi, 
 // fp16 parts of a strided matrix view: hi / lo hold [outer][ldp] halves (ldp a multiple of 8), maxbits one word that
 // receives the bit pattern of the largest finite |x| (the scale follows from it, on the device)
 int split_f16(const float *src, long s_outer, int outer, int inner, void *hi, void *lo, long ldp, unsigned *maxbits,
-              cudaStream_t st) {
+              cudaStream_t st, float bound) {
     const size_t total = (size_t)outer * ldp;
     if (!total) return B2_OK;
-    B2_CUDA(cudaMemsetAsync(maxbits, 0, sizeof(unsigned), st));
     const bool v4 = (inner % 4) == 0 && (s_outer % 4) == 0 && ((uintptr_t)src % 16) == 0;
-    {
+    if (bound > 0.0f) {
+        // the caller knows that no entry exceeds `bound`: the scale follows from it, the pass over the operand is saved
+        set_word_kernel<<<1, 1, 0, st>>>(maxbits, __float_as_uint_host(bound));
+        count_launch();
+        B2_CUDA(cudaGetLastError());
+    } else {
+        B2_CUDA(cudaMemsetAsync(maxbits, 0, sizeof(unsigned), st));
         const size_t work = v4 ? (size_t)outer * (inner / 4) : (size_t)outer * inner;
         size_t blocks = (work + 1023) / 1024;
         if (blocks > (size_t)sm_count() * 8) blocks = (size_t)sm_count() * 8;

@@ -199,8 +199,9 @@ int LstmLayerImpl::backward(const float *w, const float *x, const float *y, cons
             sD.hi = tcrec.d_hi; sD.lo = tcrec.d_lo; sD.ld = 4 * ls; sD.kmajor = true;
             sY.hi = tcrec.y_hi; sY.lo = tcrec.y_lo; sY.ld = ls; sY.kmajor = false;
         } else {
-            B2_TRY(split_operand(*scratch, bufs.deltas, 4 * ls, N, 4 * ls, true, &sD, st));
-            B2_TRY(split_operand(*scratch, y, ls, N, ls, false, &sY, st));
+            // the gate deltas are clipped to [-1, 1] (helpers/limitedError.cuh of the reference), |h| = |tanh(c) * og| < 1
+            B2_TRY(split_operand(*scratch, bufs.deltas, 4 * ls, N, 4 * ls, true, &sD, st, true, 1.0f));
+            B2_TRY(split_operand(*scratch, y, ls, N, ls, false, &sY, st, true, 1.0f));
         }
         B2_TRY(split_operand(*scratch, x, pls, N, pls, false, &sX, st, f16));
         B2_TRY(split_operand(*scratch, w, pls, 4 * ls, pls, false, &sW, st, f16));

@@ -44,6 +44,8 @@
 // leaves its loops, the cluster meets at its hardware barrier, tensor memory is released and the block returns.
 #include <cuda_fp16.h>
 
+#include <algorithm>
+#include <atomic>
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -622,10 +624,15 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                     }
                 }
                 if (ct == 0 && s > 0) PTC_TRACE(1, ti, 3);
-                if (LL && publish) {
-                    // one chunk per group: the next chunk-step is (s + 1, same chunk); collect its operand now, store afterwards
-                    gather_ll(s, ac, m_e & 1, (uint32_t)(m_e >> 1) & 1u);
-                    if (give_up_s) break;
+                if constexpr (LL) {
+                    // Collect the operand of the NEXT chunk-step now (h of that chunk's previous step), store afterwards.  With one
+                    // chunk per group that is what this step has just published, and the wait for the other blocks is part of the
+                    // chain; with two chunks it was published a whole chunk-step ago and is there already.
+                    int s_g = s, cl_g = cl;
+                    if (next_item(s_g, cl_g, ncl, Tc_s, Tmax) && s_g > 0) {
+                        gather_ll(s_g - 1, sl + cl_g * a.nslices, m_e & 1, (uint32_t)(m_e >> 1) & 1u);
+                        if (give_up_s) break;
+                    }
                     if (ct == 0 && s > 0) PTC_TRACE(1, ti, 5);
                 }
 #pragma unroll
@@ -1235,18 +1242,26 @@ __global__ void ptc_image_kernel(const float *__restrict__ wrec, const float *__
 struct Plan { int nc, nslices, nchunks, groups; bool ll; };
 // Sequences per chunk and slices per direction: as many groups of blocks as the device holds (each (direction,
 // slice) is one group's work), chunks of 32 while every group gets at most one of them, else of 64.
-Plan make_plan(int P, int D, int group_blocks) {
+// Tuning: the largest number of chunks per group that still uses the latency-optimised exchange (self-validating words
+// instead of counters and bulk copies), and the largest number of 32-sequence chunks per group before chunks become 64 wide.
+// Measured on a B200 (one layer, 200 steps, ms per sweep): forward, 64 sequences: one chunk of 64 1.46, two of 32 1.60; 128
+// sequences: counters + bulk copies 2.02, words 2.69.  Backward, 64 sequences: one chunk of 64 1.67, two of 32 1.10; 128
+// sequences: counters 3.05, words 2.44.  (The forward's cell warps collect the words themselves, the backward has warps
+// of its own for that.)  Index: 0 forward, 1 backward.
+std::atomic<int> g_ll_chunks[2] = {{1}, {2}}, g_nc32_chunks[2] = {{1}, {2}};
+
+Plan make_plan(int P, int D, int group_blocks, bool backward) {
     Plan p;
     int max_groups = sm_count() / group_blocks;
     if (max_groups < 1) max_groups = 1;
     int spd = max_groups / D;   // slices per direction that run side by side
     if (spd < 1) spd = 1;
-    p.nc = P <= 32 * spd ? 32 : 64;
+    const int llc = g_ll_chunks[backward].load(), n32r = g_nc32_chunks[backward].load(), n32 = n32r < llc ? n32r : llc;
+    p.nc = P <= 32 * spd * n32 ? 32 : 64;   // chunks of 32 exist only with the latency-optimised exchange
     p.nchunks = (P + p.nc - 1) / p.nc;
     p.nslices = p.nchunks < spd ? p.nchunks : spd;
     p.groups = D * p.nslices < max_groups ? D * p.nslices : max_groups;
-    // one chunk per group: the latency-optimised exchange (self-validating words instead of counters and bulk copies)
-    p.ll = (p.nchunks + p.nslices - 1) / p.nslices == 1;
+    p.ll = (p.nchunks + p.nslices - 1) / p.nslices <= llc;
     return p;
 }
 
@@ -1287,22 +1302,32 @@ extern "C" int b2_debug_ptc_trace(long long *out, int capacity) {
 
 bool lstm_ptc_supported(const LstmShape &s) {
     if (s.els != PTC_ELS || s.P < 1 || sm_count() < PTC_GROUP) return false;
-    const Plan pl = make_plan(s.P, s.D, PTC_GROUP);
-    const int ncl = (pl.nchunks + pl.nslices - 1) / pl.nslices;
-    return ncl <= MAXC;
+    for (int b = 0; b < 2; ++b) {
+        const Plan pl = make_plan(s.P, s.D, PTC_GROUP, b != 0);
+        if ((pl.nchunks + pl.nslices - 1) / pl.nslices > MAXC) return false;
+    }
+    return true;
+}
+
+void lstm_ptc_set_plan(bool backward, int ll_chunks, int nc32_chunks) {
+    g_ll_chunks[backward].store(ll_chunks < 1 ? 1 : ll_chunks);
+    g_nc32_chunks[backward].store(nc32_chunks < 1 ? 1 : nc32_chunks);
 }
 
 size_t lstm_ptc_image_bytes(int els, int D) { return (size_t)2 * D * 4 * els * els * 2; }   // hi + lo, fp16
 
 void lstm_ptc_exchange_sizes(int els, int P, int D, size_t *xh_bytes, size_t *xe_floats, size_t *flag_words) {
-    const Plan pl = make_plan(P, D, PTC_GROUP);
-    const size_t dch = (size_t)D * pl.nchunks;
-    // sized for either exchange: operand images / floats, or 8-byte tagged words ([2 parities][NC][els] per chunk forward,
-    // times 16 row tiles backward)
-    const size_t words = (size_t)2 * pl.nc * els;
-    *xh_bytes = dch * words * 8;            // >= the operand images (2 * 4 * 4 * NC * 128 bytes)
-    *xe_floats = dch * words * (els / 32) * 2;
-    *flag_words = dch * PTC_GROUP;
+    // sized for either exchange and for the chunking of either sweep: operand images / floats, or 8-byte tagged words
+    // ([2 parities][NC][els] per chunk forward, times 16 row tiles backward)
+    *xh_bytes = *xe_floats = *flag_words = 0;
+    for (int b = 0; b < 2; ++b) {
+        const Plan pl = make_plan(P, D, PTC_GROUP, b != 0);
+        const size_t dch = (size_t)D * pl.nchunks;
+        const size_t words = (size_t)2 * pl.nc * els;
+        *xh_bytes = std::max(*xh_bytes, dch * words * 8);            // >= the operand images (2 * 4 * 4 * NC * 128 bytes)
+        *xe_floats = std::max(*xe_floats, dch * words * (els / 32) * 2);
+        *flag_words = std::max(*flag_words, dch * PTC_GROUP);
+    }
 }
 
 int lstm_ptc_prepare(const LstmShape &s, const float *w, const PtcBuffers &pb, cudaStream_t st) {
@@ -1319,14 +1344,14 @@ int lstm_ptc_prepare(const LstmShape &s, const float *w, const PtcBuffers &pb, c
 int lstm_ptc_sweep(bool backward, const LstmShape &s, const LstmBuffers &b, const PtcBuffers &pb, const float *w, float *y,
                    const float *dy, int *status, unsigned *tag_next, cudaStream_t st) {
     if (!lstm_ptc_supported(s)) return 1;
-    const Plan pl = make_plan(s.P, s.D, PTC_GROUP);
+    const Plan pl = make_plan(s.P, s.D, PTC_GROUP, backward);
     PtcArgs a;
     a.sh = s; a.bf = b; a.w = w; a.y = y; a.dy = dy;
     a.wimg = backward ? pb.wimg_b : pb.wimg_f;
     a.scale = pb.scale; a.xh = pb.xh; a.xe = pb.xe; a.flags = pb.flags; a.status = status;
     a.tag_base = *tag_next;
     a.nslices = pl.nslices; a.nchunks = pl.nchunks;
-    // chunks of 32 only occur with one chunk per group (see make_plan)
+    // chunks of 32 only occur with the latency-optimised exchange (see make_plan)
     int rc = pl.nc == 32 ? launch<PTC_ELS, 32, true>(backward, a, pl, st)
                          : (pl.ll ? launch<PTC_ELS, 64, true>(backward, a, pl, st) : launch<PTC_ELS, 64, false>(backward, a, pl, st));
     if (rc == B2_OK) *tag_next += (unsigned)s.T + 1u;
