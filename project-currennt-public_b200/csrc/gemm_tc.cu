@@ -18,9 +18,9 @@
 //
 // Kernel.  One 128 x 128 output tile per block, K in slabs of one 128-byte swizzle row (64 halves or
 // 32 floats).  Warp 0 (one lane) feeds a 3-stage shared-memory ring with TMA (cp.async.bulk.tensor.2d,
-// SWIZZLE_128B, no multicast); warps 1 and 6 (one lane each) issue the tcgen05.mma of the main product and
+// SWIZZLE_128B, no multicast); warps 1 and 10 (one lane each) issue the tcgen05.mma of the main product and
 // of the cross terms (M=128, N=128, K=16 resp. 8; 12 per slab) on shared-memory descriptors and release
-// slots with tcgen05.commit; warps 2-5
+// slots with tcgen05.commit; warps 2-9 (two per tensor-memory lane quarter, half of the tile's columns each)
 // drain the double-buffered main accumulator from TMEM with tcgen05.ld every SEG slabs, add the
 // segments in registers and finally write C.  Operands may be K-major (k
 // contiguous) or MN-major (m resp. n contiguous); MN-major tiles are fetched as column blocks one
@@ -42,7 +42,7 @@ constexpr int BM = 128, STAGES = 3;   // the tile's N extent is a template param
 constexpr int TILE_BYTES = BM * 128;                    // 16 KiB: one operand part (hi or lo) of one stage: 128 rows of one swizzle row
 constexpr int STAGE_BYTES = 4 * TILE_BYTES;             // A_hi, A_lo, B_hi, B_lo
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024; // + slack to align the ring to 1024 B
-constexpr int NTHREADS = 224;
+constexpr int NTHREADS = 352;   // warp 0 TMA, 1 and 10 MMA issue, 2-9 epilogue
 constexpr int TC_MAX_BATCH = 8;
 // what differs between the two arithmetic modes
 template <bool F16>
@@ -201,7 +201,7 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 2); }   // both issuers release a slot
         for (int b = 0; b < 2; ++b) {
-            mbar_init(big_full(b), 1); mbar_init(big_empty(b), 4); mbar_init(x_empty(b), 4); mbar_init(x_full(b), 1);
+            mbar_init(big_full(b), 1); mbar_init(big_empty(b), 8); mbar_init(x_empty(b), 8); mbar_init(x_full(b), 1);
         }
         fail_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -263,12 +263,12 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
                 }
             }
         }
-    } else if (warp == 1 || warp == 6) {
-        // ---------------- MMA issuers: warp 1 the main products (hi*hi), warp 6 the cross terms ----------------
+    } else if (warp == 1 || warp == 10) {
+        // ---------------- MMA issuers: warp 1 the main products (hi*hi), warp 10 the cross terms ----------------
         // One thread spends about 85 cycles on issuing an MMA of this shape, more than the tensor core needs to run
         // it; two issuers with accumulators of their own keep the pipe busy and the summation order fixed.
         if (lane == 0) {
-            const bool cross = (warp == 6);
+            const bool cross = (warp == 10);
             // instruction descriptor: D=f32, A=B=tf32 (format 2) or f16 (format 0), M=128, N=BN, majors per operand
             const uint32_t fmt = F16 ? 0u : 2u;
             const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((a.a_kmajor ? 0u : 1u) << 15) |
@@ -342,7 +342,11 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
         }
     } else {
         // ---------------- epilogue: drain segments from TMEM, sum in registers, write C ----------------
+        // Eight warps: a warp may read the tensor-memory lane quarter (warp id mod 4); warps 2-5 take the first half of the
+        // tile's columns, warps 6-9 the second, so that draining a segment and storing a tile take half as long.
         const int q = warp & 3;             // TMEM lane quarter this warp may read
+        constexpr int HN = BN / 2;          // columns per warp
+        const int cbase = ((warp - 2) >> 2) * HN;
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * q) << 16);
         bool ok = true;
         int gseg = 0, it = 0;
@@ -354,9 +358,9 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
             const int kbeg = zsplit * a.kchunk;
             const int nkb = min(nkb_full, (a.K - kbeg + BK - 1) / BK);
             const int xb = it & 1;
-            float acc[BN];
+            float acc[HN];
 #pragma unroll
-            for (int j = 0; j < BN; ++j) acc[j] = 0.0f;
+            for (int j = 0; j < HN; ++j) acc[j] = 0.0f;
             const int nseg = (nkb + SEG - 1) / SEG;
             for (int seg = 0; seg < nseg; ++seg, ++gseg) {
                 const int buf = gseg & 1;
@@ -365,9 +369,9 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 32) {
+                for (int c0 = 0; c0 < HN; c0 += 32) {
                     uint32_t r[32];
-                    tmem_ld32(lane_base + (uint32_t)(buf * BN + c0), r);
+                    tmem_ld32(lane_base + (uint32_t)(buf * BN + cbase + c0), r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int j = 0; j < 32; ++j) acc[c0 + j] += __uint_as_float(r[j]);
@@ -388,9 +392,9 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < HN; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld32(lane_base + (uint32_t)(2 * BN + xb * BN + c0), r);
+                tmem_ld32(lane_base + (uint32_t)(2 * BN + xb * BN + cbase + c0), r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int j = 0; j < 32; ++j) acc[c0 + j] += F16 ? __uint_as_float(r[j]) * LO_UNSCALE : __uint_as_float(r[j]);
@@ -409,8 +413,8 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_cons
             const long ld = split ? (long)a.M : a.ldc;
             if (m < a.M) {
 #pragma unroll
-                for (int j = 0; j < BN; ++j) {
-                    const int n = n0 + j;
+                for (int j = 0; j < HN; ++j) {
+                    const int n = n0 + cbase + j;
                     if (n < a.N) {
                         float *p = dst + (size_t)n * ld + m;
                         float v = F16 ? acc[j] * inv_a * inv_b : acc[j];

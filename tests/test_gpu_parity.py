@@ -206,6 +206,42 @@ def test_persistent_tensor_core_recurrence(ls, bi, P, lens, mode):
             assert np.array_equal(np.asarray(got[key]), np.asarray(again[key])), "not deterministic: " + key
 
 
+@pytest.mark.parametrize("P,lens", [(40, [9] * 20 + [8] * 10 + [5] * 10), (64, [7] * 40 + [6] * 20 + [2] * 4),
+                                    (100, [6] * 70 + [4] * 30), (130, [5] * 128 + [3, 2])])
+def test_chunk_plans_of_the_tensor_core_recurrence_agree(P, lens):
+    """b2_config_set_ptc_plan changes how the sequences of a fraction are grouped into chunks and which exchange
+    carries h and the partial errors between the blocks (step counters + bulk copies, or self-validating words; one,
+    two or more chunks in flight).  The arithmetic per cell does not depend on it: every plan must give the same bits,
+    and the default plan must agree with the reference."""
+    from b2lstm import workloads
+    from b2lstm.lib import lib
+    layers = L(("input", 16), ("blstm", 1024), ("feedforward_identity", 8), ("sse", 8))
+    lens = np.array(lens, np.int32)
+    x, tg = workloads.make_fraction(16, 8, P, lens, 71, 72)
+    w = workloads.make_weights(layers, 73, 0.08)
+    want = run_kind(checker(), layers, P, lens, x, tg, w)
+    runs = {}
+    try:
+        for plan in [None, (1, 1), (2, 1), (2, 2), (3, 2)]:
+            if plan is None:
+                lib().b2_config_set_ptc_plan(0, 1, 1)
+                lib().b2_config_set_ptc_plan(1, 2, 2)
+            else:
+                for backward in (0, 1):
+                    lib().b2_config_set_ptc_plan(backward, plan[0], plan[1])
+            paths = {}
+            runs[plan] = run_gpu(layers, P, lens, x, tg, w, dict(recurrence=5, ffma=0), paths=paths)
+            assert paths[1] == ("persistent_tensor_core", "persistent_tensor_core"), paths
+    finally:
+        lib().b2_config_set_ptc_plan(0, 1, 1)
+        lib().b2_config_set_ptc_plan(1, 2, 2)
+    parity.compare_run(layers, runs[None], want, "default plan, P%d" % P, lstm_pad_zero_lens=lens)
+    for plan, got in runs.items():
+        for key in got:
+            if key != "launches":
+                assert np.array_equal(np.asarray(got[key]), np.asarray(runs[None][key])), (plan, key)
+
+
 def test_persistent_tensor_core_recurrence_with_large_weights_and_activations():
     """Recurrent weights far from the usual range (one direction scaled by 40, the other by 1/300) and targets
     that drive the deltas into the clip: the per-direction power-of-two scale of the fp16 operands must keep
