@@ -91,6 +91,11 @@ __device__ long long g_ptc_trace[2][TRACE_ROLES][TRACE_ITEMS][TRACE_SLOTS];   //
 #define PTC_TRACE(role, item, slot) do { } while (0)
 #define PTC_TRACE_B(role, item, slot) do { } while (0)
 #endif
+#if defined(B2_PTC_TRACE) && defined(B2_PTC_TRACE_CELL)
+#define PTC_TRACE_C(role, item, slot) PTC_TRACE(role, item, slot)
+#else
+#define PTC_TRACE_C(role, item, slot) do { } while (0)
+#endif
 
 struct PtcArgs {
     LstmShape sh;
@@ -392,6 +397,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                 if (warp == 2 && lane == 0) PTC_TRACE(3, ti, 0);
                 // the partial sums of the item before last have been read, here and in the peers this warp writes to
                 bool ok = mbar_wait_bounded<true>(z_free(buf), ph ^ 1u, &give_up_s, WAIT_CYCLES);
+                if (warp == 2 && lane == 0) PTC_TRACE(3, ti, 3);
                 if (warp == 2 && lane == 0) mbar_expect_tx(z_full(buf), (uint32_t)(KS - 1) * G::ZBLK);
                 ok = ok && mbar_wait_bounded<false>(acc_full(buf), ph, &give_up_s, WAIT_CYCLES);
                 if (!__all_sync(0xffffffffu, ok)) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
@@ -550,10 +556,10 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                     const int buf = m_e & 1;
                     const uint32_t ph = (uint32_t)(m_e >> 1) & 1u;
                     ++m_e;
-                    if (ct == 0) PTC_TRACE(1, ti, 0);
+                    if (ct == 0) PTC_TRACE_C(1, ti, 0);
                     const bool ok = mbar_wait_bounded<true>(z_full(buf), ph, &give_up_s, WAIT_CYCLES);
                     if (!__all_sync(0xffffffffu, ok)) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
-                    if (ct == 0) PTC_TRACE(1, ti, 1);
+                    if (ct == 0) PTC_TRACE_C(1, ti, 1);
                     // partial sums of the contraction slices in slice order (own slice from zown, the others' as received)
                     const float *zown = reinterpret_cast<const float *>(gbase + G::F_ZOWN + (uint32_t)buf * G::ZBLK);
                     const float *zrecv = reinterpret_cast<const float *>(gbase + G::F_ZRECV + (uint32_t)(buf * (KS - 1)) * G::ZBLK);
@@ -571,7 +577,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                     __syncwarp();
                     if (lane == 0) mbar_arrive(z_free(buf));
                     else if (lane < KS) mbar_arrive_cluster_relaxed(map_to_rank(z_free(buf), (uint32_t)((q + lane) & (KS - 1))));
-                    if (ct == 0) PTC_TRACE(1, ti, 2);
+                    if (ct == 0) PTC_TRACE_C(1, ti, 2);
                 }
                 const bool first = (s == 0), publish = (s + 1 < Tc_s[cl]);
                 unsigned char *img = a.xh + ((dch + ac) * 2 + (s & 1)) * (size_t)(KS * G::B_BUF) + (size_t)qs * G::B_BUF + img_cb;
@@ -611,7 +617,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                         }
                     }
                 }
-                if (ct == 0 && s > 0) PTC_TRACE(1, ti, 6);
+                if (ct == 0 && s > 0) PTC_TRACE_C(1, ti, 6);
                 if (publish && !LL) {
                     // this warp's part of h[t] is on its way: hand it to the publisher; the layer's own state is stored afterwards
                     const int pb = m_p & 1;
@@ -623,7 +629,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                         mbar_arrive(rel_full(pb));
                     }
                 }
-                if (ct == 0 && s > 0) PTC_TRACE(1, ti, 3);
+                if (ct == 0 && s > 0) PTC_TRACE_C(1, ti, 3);
                 if constexpr (LL) {
                     // Collect the operand of the NEXT chunk-step now (h of that chunk's previous step), store afterwards.  With one
                     // chunk per group that is what this step has just published, and the wait for the other blocks is part of the
@@ -633,7 +639,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                         gather_ll(s_g - 1, sl + cl_g * a.nslices, m_e & 1, (uint32_t)(m_e >> 1) & 1u);
                         if (give_up_s) break;
                     }
-                    if (ct == 0 && s > 0) PTC_TRACE(1, ti, 5);
+                    if (ct == 0 && s > 0) PTC_TRACE_C(1, ti, 5);
                 }
 #pragma unroll
                 for (int i = 0; i < CPT; ++i) {
@@ -646,7 +652,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                         a.y[f * ls + u] = hh[i];
                     }
                 }
-                if (ct == 0 && s > 0) PTC_TRACE(1, ti, 7);
+                if (ct == 0 && s > 0) PTC_TRACE_C(1, ti, 7);
                 if constexpr (LL) {
                     more = next_item(s, cl, ncl, Tc_s, Tmax);
                     if (more) fetch(s, cl);
@@ -660,7 +666,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                         cpv[i] = same_chunk ? cs[i] : cpv_n[i];
                     }
                 }
-                if (ct == 0 && s > 1) PTC_TRACE(1, ti, 4);
+                if (ct == 0 && s > 1) PTC_TRACE_C(1, ti, 4);
             }
             // frames beyond a chunk's longest sequence are padding for all its sequences: outputs are zero there
             for (int c2 = 0; c2 < ncl; ++c2) {
