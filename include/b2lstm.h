@@ -161,11 +161,12 @@ int b2_net_create(const char *network_json, int parallel_sequences, int max_seq_
 void b2_config_set_lstm_forget_gate_bias(float value);
 
 /* Tuning of the persistent tensor-core recurrence (no counterpart in the reference).  The sequences of a fraction are
- * processed in chunks; the chunks of a group of blocks are in flight together.  ll_chunks = the largest number of chunks
- * per group that still uses the latency-optimised exchange (self-validating words through L2 instead of step counters
- * and bulk copies); nc32_chunks = the largest number of chunks per group that are 32 sequences wide (wider fractions use
- * chunks of 64).  The forward (backward = 0) and the backward sweep have settings of their own (defaults 1, 1 and 2, 2: the
- * measured optimum on a B200).  Call before layers or networks are created. */
+ * processed in chunks of 32 or 64; the chunks of a group of blocks are in flight together.  nc32_chunks = the largest
+ * number of chunks per group for which chunks are 32 sequences wide (wider fractions use chunks of 64); chunks of 32
+ * always use the latency-optimised exchange (self-validating words through L2 instead of step counters and bulk copies).
+ * ll_chunks = the largest number of 64-wide chunks per group that still uses that exchange.  The forward (backward = 0)
+ * and the backward sweep have settings of their own (defaults 1, 1 and 2, 5: the measured optimum on a B200).  Every
+ * setting gives the same bits.  Call before layers or networks are created. */
 void b2_config_set_ptc_plan(int backward, int ll_chunks, int nc32_chunks);
 void b2_net_destroy(b2_net *net);
 /* Layer::parallelSequences() / Layer::maxSeqLength() (layers/Layer.hpp:163-175) the net was created with */

@@ -188,7 +188,9 @@ struct Geo {
     static constexpr uint32_t B_HL = 2 * NC * 128, B_BUF = 2 * B_HL;    // operand B: [hi/lo][2 column blocks][NC rows x 128 B]
     // forward
     static constexpr uint32_t F_B = A_BYTES, F_ZOWN = F_B + 2 * B_BUF, F_ZRECV = F_ZOWN + 2 * ZBLK;
-    static constexpr uint32_t F_END = F_ZRECV + 2 * (KS - 1) * ZBLK;
+    // staging of the tagged words of one operand (chunks of 32 sequences with several chunks per group: gather warps)
+    static constexpr uint32_t F_STAGE = F_ZRECV + 2 * (KS - 1) * ZBLK;
+    static constexpr uint32_t F_END = F_STAGE + (NC == 32 ? NC * 1024 : 0);
     // backward
     static constexpr uint32_t B_B = A_BYTES, B_ESUM = B_B + 2 * B_BUF;
     // what a cell hands to its own next step (forget gate, cell error, two gate deltas), for up to CARRY chunks per group
@@ -230,7 +232,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
     constexpr int RT = G::RT, CPT = NC / (4 * CW);   // a cell warp covers 8 units x 4 sequences
     static_assert(CPT >= 1, "more cell warps than cells");
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) u64 bars[16];
+    __shared__ __align__(8) u64 bars[17];
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int give_up_s;
     __shared__ int lens_s[MAXC * NC], Tc_s[MAXC], Tmax_s;
@@ -247,6 +249,12 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
     auto acc_free = [&](int b) { return bar0 + 8u * (uint32_t)(6 + b); };  // drain warps -> MMA
     auto z_full = [&](int b) { return bar0 + 8u * (uint32_t)(8 + b); };    // own and the peers' partial sums are in -> cell warps
     auto z_free = [&](int b) { return bar0 + 8u * (uint32_t)(10 + b); };   // cell warps of the whole cluster have read them -> drain warps
+    const uint32_t stage_bar = bar0 + 8u * 16u;                             // bulk copies of tagged words -> gather warps
+    // Chunks of 32 sequences with several chunks per group: the operand of a chunk-step was published a whole chunk-step
+    // earlier, so two otherwise idle warps collect it (bulk copies of the tagged words into a staging area, validation and
+    // repacking from there) while the cell warps work on the other chunks.  With one chunk per group the cell warps collect
+    // it themselves, word by word, right after publishing (lowest latency).
+    const bool gw = LL && NC == 32 && (a.nchunks + a.nslices - 1) / a.nslices >= 2;
 
     const int P = a.sh.P, T = a.sh.T, ls = a.sh.ls, D = a.sh.D;
     const int grp = blockIdx.x / G::GROUP, ngroups = gridDim.x / G::GROUP;
@@ -256,11 +264,12 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
 
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
-            mbar_init(b_full(b), LL ? CW : 1); mbar_init(b_free(b), 2); mbar_init(acc_full(b), 2); mbar_init(acc_free(b), 4);
+            mbar_init(b_full(b), LL && !gw ? CW : 1); mbar_init(b_free(b), 2); mbar_init(acc_full(b), 2); mbar_init(acc_free(b), 4);
             mbar_init(z_full(b), 5);           // 4 drain warps + the arrival that announces the peers' bytes
             mbar_init(z_free(b), CW * KS);     // every cell warp of every block of the cluster
             mbar_init(rel_full(b), CW); mbar_init(rel_free(b), 1);
         }
+        mbar_init(stage_bar, 1);
         give_up_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -274,6 +283,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
 
     int m_g = 0, m_m = 0, m_d = 0, m_e = 0;   // running count of MMA items per role (buffer = count & 1)
     int m_p = 0;                             // running count of published chunk-steps (cell warps and publisher)
+    uint32_t st_ph = 0;                      // phase of the staging barrier (gather warps)
     const int nwork = D * a.nslices;
     for (int wi = grp; wi < nwork; wi += ngroups) {
         const int d = wi % D, sl = wi / D;
@@ -324,6 +334,64 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                     mma_commit(b_free(buf));
                     mma_commit(acc_full(buf));
                     if (hh == 0) PTC_TRACE(0, ti, 2);
+                }
+            }
+        } else if (gw && (warp == 1 || warp == 6 + CW)) {
+            // ------------------------------------ gather warps: tagged words of h[t-1] -> operand B ------------------------------------
+            if constexpr (LL && NC == 32) {
+                const int gt = (warp == 1 ? 0 : 32) + lane;          // 64 gather threads
+                int s = 0, cl = -1;
+                while (next_item(s, cl, ncl, Tc_s, Tmax)) {
+                    if (s == 0) continue;
+                    if (give_up_s) break;
+                    const int buf = m_g & 1;
+                    const uint32_t ph = (uint32_t)(m_g >> 1) & 1u;
+                    ++m_g;
+                    const int ac = sl + cl * a.nslices;
+                    // operand buffer buf: the MMAs of the chunk-step before last have read it (the gather threads go on together or not at all)
+                    bool ok = mbar_wait_bounded<false>(b_free(buf), ph ^ 1u, &give_up_s, WAIT_CYCLES);
+                    if (bar_named_or(1, 64, !ok)) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
+                    const u64 *src = reinterpret_cast<const u64 *>(a.xh) + ((dch + ac) * 2 + ((s - 1) & 1)) * (size_t)(NC * ELS) + KSL * q;
+                    const unsigned tag = a.tag_base + (unsigned)(s - 1);
+                    const uint32_t bb = sbase + G::F_B + (uint32_t)buf * G::B_BUF;
+                    const uint32_t stg = sbase + G::F_STAGE;
+                    for (unsigned round = 0;; ++round) {
+                        // one row of 128 words (this block's contraction slice of one sequence) per copy; then wait for all of them
+                        if (gt == 0) mbar_expect_tx(stage_bar, NC * 1024u);
+                        if (gt < NC) bulk_g2s(stg + (uint32_t)gt * 1024u, src + (size_t)gt * ELS, 1024u, stage_bar);
+                        ok = mbar_wait_bounded<false>(stage_bar, st_ph, &give_up_s, WAIT_CYCLES);
+                        st_ph ^= 1u;
+                        bool all = ok;
+                        if (ok) {
+#pragma unroll 2
+                            for (int i = 0; i < NC * 16 / 64; ++i) {
+                                const int ci = gt + 64 * i, n = ci >> 4, kc = ci & 15;
+                                const uint4 *sp = reinterpret_cast<const uint4 *>(gbase + G::F_STAGE + n * 1024 + kc * 64);
+                                const uint4 w01 = sp[0], w23 = sp[1], w45 = sp[2], w67 = sp[3];   // {payload, tag} pairs
+                                const bool valid = w01.y == tag && w01.w == tag && w23.y == tag && w23.w == tag && w45.y == tag &&
+                                                   w45.w == tag && w67.y == tag && w67.w == tag;
+                                if (!valid) { all = false; continue; }
+                                const uint32_t pl[8] = {w01.x, w01.z, w23.x, w23.z, w45.x, w45.z, w67.x, w67.z};   // hi | lo << 16
+                                uint32_t hi[4], lo[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    hi[e] = (pl[2 * e] & 0xffffu) | (pl[2 * e + 1] << 16);
+                                    lo[e] = (pl[2 * e] >> 16) | (pl[2 * e + 1] & 0xffff0000u);
+                                }
+                                const uint32_t o = (uint32_t)(kc >> 3) * (NC * 128u) + (uint32_t)n * 128u + (uint32_t)(((kc & 7) ^ (n & 7)) * 16);
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(bb + o), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(bb + G::B_HL + o), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
+                            }
+                        }
+                        // every gather thread is through the staging area; repeat while a word did not show the step's tag yet
+                        if (!bar_named_or(1, 64, !all)) break;
+                        if (!ok || round >= POLL_LIMIT || give_up_s || ((round & 255u) == 255u && ld_relaxed_s32(a.status) != 0)) ok = false;
+                        if (bar_named_or(1, 64, !ok)) { ok = false; break; }
+                    }
+                    if (!ok) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
+                    fence_async_smem();
+                    bar_named(1, 64);
+                    if (gt == 0) mbar_arrive(b_full(buf));
                 }
             }
         } else if (warp == 1) {
@@ -635,7 +703,7 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                     // chunk per group that is what this step has just published, and the wait for the other blocks is part of the
                     // chain; with two chunks it was published a whole chunk-step ago and is there already.
                     int s_g = s, cl_g = cl;
-                    if (next_item(s_g, cl_g, ncl, Tc_s, Tmax) && s_g > 0) {
+                    if (!gw && next_item(s_g, cl_g, ncl, Tc_s, Tmax) && s_g > 0) {
                         gather_ll(s_g - 1, sl + cl_g * a.nslices, m_e & 1, (uint32_t)(m_e >> 1) & 1u);
                         if (give_up_s) break;
                     }
@@ -1248,13 +1316,16 @@ __global__ void ptc_image_kernel(const float *__restrict__ wrec, const float *__
 struct Plan { int nc, nslices, nchunks, groups; bool ll; };
 // Sequences per chunk and slices per direction: as many groups of blocks as the device holds (each (direction,
 // slice) is one group's work), chunks of 32 while every group gets at most one of them, else of 64.
-// Tuning: the largest number of chunks per group that still uses the latency-optimised exchange (self-validating words
-// instead of counters and bulk copies), and the largest number of 32-sequence chunks per group before chunks become 64 wide.
-// Measured on a B200 (one layer, 200 steps, ms per sweep): forward, 64 sequences: one chunk of 64 1.46, two of 32 1.60; 128
-// sequences: counters + bulk copies 2.02, words 2.69.  Backward, 64 sequences: one chunk of 64 1.67, two of 32 1.10; 128
-// sequences: counters 3.05, words 2.44.  (The forward's cell warps collect the words themselves, the backward has warps
-// of its own for that.)  Index: 0 forward, 1 backward.
-std::atomic<int> g_ll_chunks[2] = {{1}, {2}}, g_nc32_chunks[2] = {{1}, {2}};
+// Tuning (index 0 forward, 1 backward): nc32 = the largest number of chunks per group for which chunks are 32 sequences
+// wide (such chunks always use the latency-optimised exchange: self-validating words instead of counters and bulk
+// copies); ll = the largest number of 64-wide chunks per group that still uses that exchange.
+// Measured on a B200 (one layer, 200 steps, ms per sweep).  Forward, 64 sequences: one chunk of 64 1.45, two of 32 1.52;
+// 128 sequences: two chunks of 64 behind counters 1.95, with words 2.69, four of 32 2.47 (the forward's operand is collected
+// by its cell warps, or for several 32-wide chunks by two gather warps: neither overlaps well with a second chunk).
+// Backward (warps of its own collect the partial errors), 64 sequences: one chunk of 64 1.67, two of 32 1.10; 96: 2.28 /
+// 1.50; 128: two of 64 behind counters 3.05, with words 2.45, four of 32 2.00; 160: three of 64 2.76, five of 32 2.54;
+// 192: three of 64 2.99, six of 32 3.11; 256: four of 64 2.70, eight of 32 4.77.
+std::atomic<int> g_ll_chunks[2] = {{1}, {2}}, g_nc32_chunks[2] = {{1}, {5}};
 
 Plan make_plan(int P, int D, int group_blocks, bool backward) {
     Plan p;
@@ -1262,12 +1333,12 @@ Plan make_plan(int P, int D, int group_blocks, bool backward) {
     if (max_groups < 1) max_groups = 1;
     int spd = max_groups / D;   // slices per direction that run side by side
     if (spd < 1) spd = 1;
-    const int llc = g_ll_chunks[backward].load(), n32r = g_nc32_chunks[backward].load(), n32 = n32r < llc ? n32r : llc;
-    p.nc = P <= 32 * spd * n32 ? 32 : 64;   // chunks of 32 exist only with the latency-optimised exchange
+    const int llc = g_ll_chunks[backward].load(), n32 = g_nc32_chunks[backward].load();
+    p.nc = P <= 32 * spd * n32 ? 32 : 64;   // chunks of 32 always use the latency-optimised exchange
     p.nchunks = (P + p.nc - 1) / p.nc;
     p.nslices = p.nchunks < spd ? p.nchunks : spd;
     p.groups = D * p.nslices < max_groups ? D * p.nslices : max_groups;
-    p.ll = (p.nchunks + p.nslices - 1) / p.nslices <= llc;
+    p.ll = p.nc == 32 || (p.nchunks + p.nslices - 1) / p.nslices <= llc;
     return p;
 }
 

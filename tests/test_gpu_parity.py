@@ -210,8 +210,8 @@ def test_persistent_tensor_core_recurrence(ls, bi, P, lens, mode):
                                     (100, [6] * 70 + [4] * 30), (130, [5] * 128 + [3, 2])])
 def test_chunk_plans_of_the_tensor_core_recurrence_agree(P, lens):
     """b2_config_set_ptc_plan changes how the sequences of a fraction are grouped into chunks and which exchange
-    carries h and the partial errors between the blocks (step counters + bulk copies, or self-validating words; one,
-    two or more chunks in flight).  The arithmetic per cell does not depend on it: every plan must give the same bits,
+    carries h and the partial errors between the blocks (step counters + bulk copies, or self-validating words collected
+    by the cell warps or by gather warps; one, two or more chunks in flight).  The arithmetic per cell does not depend on it: every plan must give the same bits,
     and the default plan must agree with the reference."""
     from b2lstm import workloads
     from b2lstm.lib import lib
@@ -222,10 +222,10 @@ def test_chunk_plans_of_the_tensor_core_recurrence_agree(P, lens):
     want = run_kind(checker(), layers, P, lens, x, tg, w)
     runs = {}
     try:
-        for plan in [None, (1, 1), (2, 1), (2, 2), (3, 2)]:
+        for plan in [None, (1, 1), (2, 1), (2, 2), (1, 4), (3, 3)]:
             if plan is None:
                 lib().b2_config_set_ptc_plan(0, 1, 1)
-                lib().b2_config_set_ptc_plan(1, 2, 2)
+                lib().b2_config_set_ptc_plan(1, 2, 5)
             else:
                 for backward in (0, 1):
                     lib().b2_config_set_ptc_plan(backward, plan[0], plan[1])
@@ -234,7 +234,7 @@ def test_chunk_plans_of_the_tensor_core_recurrence_agree(P, lens):
             assert paths[1] == ("persistent_tensor_core", "persistent_tensor_core"), paths
     finally:
         lib().b2_config_set_ptc_plan(0, 1, 1)
-        lib().b2_config_set_ptc_plan(1, 2, 2)
+        lib().b2_config_set_ptc_plan(1, 2, 5)
     parity.compare_run(layers, runs[None], want, "default plan, P%d" % P, lstm_pad_zero_lens=lens)
     for plan, got in runs.items():
         for key in got:
