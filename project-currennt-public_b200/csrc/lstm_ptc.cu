@@ -355,6 +355,18 @@ __global__ void __launch_bounds__(fwd_threads(LL), 1) lstm_fwd_ptc_kernel(PtcArg
                     const unsigned tag = a.tag_base + (unsigned)(s - 1);
                     const uint32_t bb = sbase + G::F_B + (uint32_t)buf * G::B_BUF;
                     const uint32_t stg = sbase + G::F_STAGE;
+                    // Cheap wait first: one word per gather thread (of each of the 16 source blocks, the sequences their cell warps
+                    // publish last) until it shows the step's tag; a round of bulk copies that comes too early costs far more.
+                    {
+                        const u64 *sw = src + (size_t)(NC - 1 - (gt >> 4)) * ELS + 8 * (gt & 15) + 6;
+                        for (unsigned round = 0; ok; ++round) {
+                            u64 w0, w1;
+                            ld_tagged2(sw, w0, w1);
+                            if ((unsigned)(w0 >> 32) == tag && (unsigned)(w1 >> 32) == tag) break;
+                            if (round >= POLL_LIMIT || give_up_s || ((round & 1023u) == 1023u && ld_relaxed_s32(a.status) != 0)) ok = false;
+                        }
+                        if (bar_named_or(1, 64, !ok)) { give_up_s = 1; atomicCAS(a.status, 0, (int)B2_ERR_STEP_TIMEOUT); break; }
+                    }
                     for (unsigned round = 0;; ++round) {
                         // one row of 128 words (this block's contraction slice of one sequence) per copy; then wait for all of them
                         if (gt == 0) mbar_expect_tx(stage_bar, NC * 1024u);
