@@ -161,13 +161,15 @@ int b2_net_create(const char *network_json, int parallel_sequences, int max_seq_
 void b2_config_set_lstm_forget_gate_bias(float value);
 
 /* Tuning of the persistent tensor-core recurrence (no counterpart in the reference).  The sequences of a fraction are
- * processed in chunks of 32 or 64; the chunks of a group of blocks are in flight together.  nc32_chunks = the largest
- * number of chunks per group for which chunks are 32 sequences wide (wider fractions use chunks of 64); chunks of 32
- * always use the latency-optimised exchange (self-validating words through L2 instead of step counters and bulk copies).
- * ll_chunks = the largest number of 64-wide chunks per group that still uses that exchange.  The forward (backward = 0)
- * and the backward sweep have settings of their own (defaults 1, 1 and 2, 5: the measured optimum on a B200).  Every
- * setting gives the same bits.  Call before layers or networks are created. */
-void b2_config_set_ptc_plan(int backward, int ll_chunks, int nc32_chunks);
+ * processed in chunks of 32 or 64; the chunks of a group of blocks are in flight together.
+ *   nc32_chunks: the largest number of chunks per group for which chunks are 32 sequences wide and use the
+ *     latency-optimised exchange (self-validating words through L2 instead of step counters and bulk copies);
+ *   ll_chunks: the largest number of 64-wide chunks per group that still uses that exchange;
+ *   nc32_counter_chunks (backward sweep only, 0 = off): the largest number of 32-wide chunks per group that run behind
+ *     step counters; wider fractions use chunks of 64 behind step counters.
+ * The forward (backward = 0) and the backward sweep have settings of their own (defaults 1, 1, 0 and 2, 5, 6: the measured
+ * optimum on a B200).  Every setting gives the same bits.  Call before layers or networks are created. */
+void b2_config_set_ptc_plan(int backward, int ll_chunks, int nc32_chunks, int nc32_counter_chunks);
 void b2_net_destroy(b2_net *net);
 /* Layer::parallelSequences() / Layer::maxSeqLength() (layers/Layer.hpp:163-175) the net was created with */
 int b2_net_parallel_sequences(const b2_net *net);

@@ -47,7 +47,7 @@ SIGNATURES = {
     "b2_lstm_synchronize": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b2_net_create": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_uint, C.POINTER(C.c_void_p)]),
     "b2_config_set_lstm_forget_gate_bias": (None, [C.c_float]),
-    "b2_config_set_ptc_plan": (None, [C.c_int, C.c_int, C.c_int]),
+    "b2_config_set_ptc_plan": (None, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "b2_net_destroy": (None, [C.c_void_p]),
     "b2_net_parallel_sequences": (C.c_int, [C.c_void_p]),
     "b2_net_max_seq_length": (C.c_int, [C.c_void_p]),

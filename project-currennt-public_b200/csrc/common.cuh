@@ -191,7 +191,7 @@ struct PtcBuffers {
 };
 bool lstm_ptc_supported(const LstmShape &s);
 size_t lstm_ptc_image_bytes(int els, int D);
-void lstm_ptc_set_plan(bool backward, int ll_chunks, int nc32_chunks);
+void lstm_ptc_set_plan(bool backward, int ll_chunks, int nc32_chunks, int nc32_counter_chunks);
 void lstm_ptc_exchange_sizes(int els, int P, int D, size_t *xh_bytes, size_t *xe_floats, size_t *flag_words);
 int lstm_ptc_prepare(const LstmShape &s, const float *w, const PtcBuffers &pb, cudaStream_t st);
 int lstm_ptc_sweep(bool backward, const LstmShape &s, const LstmBuffers &b, const PtcBuffers &pb, const float *w, float *y,

@@ -552,7 +552,7 @@ __global__ void __launch_bounds__(256) absmax_kernel(const float *__restrict__ s
     }
 }
 __global__ void set_word_kernel(unsigned *dst, unsigned v) { *dst = v; }
-inline unsigned __float_as_uint_host(float f) { unsigned u; memcpy(&u, &f, sizeof u); return u; }
+inline unsigned float_bits(float f) { unsigned u; memcpy(&u, &f, sizeof u); return u; }
 // x*S = hi + lo * 2^-11; both parts as fp16 bit patterns
 __device__ __forceinline__ void split_f16_one(float x, float S, unsigned short &h, unsigned short &l) {
     const float xs = x * S;
@@ -692,7 +692,7 @@ int split_f16(const float *src, long s_outer, int outer, int inner, void *hi, vo
     const bool v4 = (inner % 4) == 0 && (s_outer % 4) == 0 && ((uintptr_t)src % 16) == 0;
     if (bound > 0.0f) {
         // the caller knows that no entry exceeds `bound`: the scale follows from it, the pass over the operand is saved
-        set_word_kernel<<<1, 1, 0, st>>>(maxbits, __float_as_uint_host(bound));
+        set_word_kernel<<<1, 1, 0, st>>>(maxbits, float_bits(bound));
         count_launch();
         B2_CUDA(cudaGetLastError());
     } else {

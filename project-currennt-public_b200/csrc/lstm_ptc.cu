@@ -194,7 +194,7 @@ struct Geo {
     // backward
     static constexpr uint32_t B_B = A_BYTES, B_ESUM = B_B + 2 * B_BUF;
     // what a cell hands to its own next step (forget gate, cell error, two gate deltas), for up to CARRY chunks per group
-    static constexpr int CARRY = 4;
+    static constexpr int CARRY = NC == 32 ? 8 : 4;
     static constexpr uint32_t B_CARRY = B_ESUM + 2 * NC * UPC * 4;
     static constexpr uint32_t B_END = B_CARRY + CARRY * 4 * NC * UPC * 4;
     static constexpr size_t fwd_smem() { return F_END + 1024; }
@@ -1338,6 +1338,8 @@ struct Plan { int nc, nslices, nchunks, groups; bool ll; };
 // 1.50; 128: two of 64 behind counters 3.05, with words 2.45, four of 32 2.00; 160: three of 64 2.76, five of 32 2.54;
 // 192: three of 64 2.99, six of 32 3.11; 256: four of 64 2.70, eight of 32 4.77.
 std::atomic<int> g_ll_chunks[2] = {{1}, {2}}, g_nc32_chunks[2] = {{1}, {5}};
+// backward only: the largest number of 32-wide chunks per group that run behind counters (wider fractions use chunks of 64)
+std::atomic<int> g_nc32_counter_chunks{6};   // 192 sequences: three chunks of 64 2.73 ms, six of 32 2.52; 256: four of 64 2.69, eight of 32 3.21
 
 Plan make_plan(int P, int D, int group_blocks, bool backward) {
     Plan p;
@@ -1346,26 +1348,31 @@ Plan make_plan(int P, int D, int group_blocks, bool backward) {
     int spd = max_groups / D;   // slices per direction that run side by side
     if (spd < 1) spd = 1;
     const int llc = g_ll_chunks[backward].load(), n32 = g_nc32_chunks[backward].load();
-    p.nc = P <= 32 * spd * n32 ? 32 : 64;   // chunks of 32 always use the latency-optimised exchange
+    const int n32c = backward ? g_nc32_counter_chunks.load() : 0;
+    const bool words32 = P <= 32 * spd * n32;           // chunks of 32 with the latency-optimised exchange
+    p.nc = (words32 || P <= 32 * spd * n32c) ? 32 : 64;
     p.nchunks = (P + p.nc - 1) / p.nc;
     p.nslices = p.nchunks < spd ? p.nchunks : spd;
     p.groups = D * p.nslices < max_groups ? D * p.nslices : max_groups;
-    p.ll = p.nc == 32 || (p.nchunks + p.nslices - 1) / p.nslices <= llc;
+    p.ll = p.nc == 32 ? words32 : (p.nchunks + p.nslices - 1) / p.nslices <= llc;
     return p;
 }
 
-template <int ELS, int NC, bool LL>
-int launch(bool backward, PtcArgs &a, const Plan &pl, cudaStream_t st) {
+template <int ELS, int NC, bool LL, bool BWD>
+int launch_dir(PtcArgs &a, const Plan &pl, cudaStream_t st) {
     typedef Geo<ELS, NC> G;
-    void (*kern)(PtcArgs) = backward ? lstm_bwd_ptc_kernel<ELS, NC, LL> : lstm_fwd_ptc_kernel<ELS, NC, LL>;
-    const size_t smem = backward ? G::bwd_smem() : G::fwd_smem();
+    void (*kern)(PtcArgs);
+    size_t smem;
+    int threads;
+    if constexpr (BWD) { kern = lstm_bwd_ptc_kernel<ELS, NC, LL>; smem = G::bwd_smem(); threads = bwd_threads(LL); }
+    else { kern = lstm_fwd_ptc_kernel<ELS, NC, LL>; smem = G::fwd_smem(); threads = fwd_threads(LL); }
     B2_TRY(set_max_dynamic_smem((const void *)kern, (int)smem));
     cudaLaunchConfig_t cfg = cudaLaunchConfig_t{};
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = KS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.gridDim = dim3(pl.groups * G::GROUP);
-    cfg.blockDim = dim3(backward ? bwd_threads(LL) : fwd_threads(LL));
+    cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cfg.attrs = attr;
@@ -1373,6 +1380,10 @@ int launch(bool backward, PtcArgs &a, const Plan &pl, cudaStream_t st) {
     B2_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
     count_launch();
     return B2_OK;
+}
+template <int ELS, int NC, bool LL>
+int launch(bool backward, PtcArgs &a, const Plan &pl, cudaStream_t st) {
+    return backward ? launch_dir<ELS, NC, LL, true>(a, pl, st) : launch_dir<ELS, NC, LL, false>(a, pl, st);
 }
 
 constexpr int PTC_ELS = 512;
@@ -1398,9 +1409,10 @@ bool lstm_ptc_supported(const LstmShape &s) {
     return true;
 }
 
-void lstm_ptc_set_plan(bool backward, int ll_chunks, int nc32_chunks) {
+void lstm_ptc_set_plan(bool backward, int ll_chunks, int nc32_chunks, int nc32_counter_chunks) {
     g_ll_chunks[backward].store(ll_chunks < 1 ? 1 : ll_chunks);
     g_nc32_chunks[backward].store(nc32_chunks < 1 ? 1 : nc32_chunks);
+    if (backward) g_nc32_counter_chunks.store(nc32_counter_chunks < 0 ? 0 : nc32_counter_chunks);
 }
 
 size_t lstm_ptc_image_bytes(int els, int D) { return (size_t)2 * D * 4 * els * els * 2; }   // hi + lo, fp16
@@ -1441,8 +1453,10 @@ int lstm_ptc_sweep(bool backward, const LstmShape &s, const LstmBuffers &b, cons
     a.tag_base = *tag_next;
     a.nslices = pl.nslices; a.nchunks = pl.nchunks;
     // chunks of 32 only occur with the latency-optimised exchange (see make_plan)
-    int rc = pl.nc == 32 ? launch<PTC_ELS, 32, true>(backward, a, pl, st)
-                         : (pl.ll ? launch<PTC_ELS, 64, true>(backward, a, pl, st) : launch<PTC_ELS, 64, false>(backward, a, pl, st));
+    int rc;
+    if (pl.nc == 32 && !pl.ll) rc = launch_dir<PTC_ELS, 32, false, true>(a, pl, st);   // backward sweep only (make_plan)
+    else if (pl.nc == 32) rc = launch<PTC_ELS, 32, true>(backward, a, pl, st);
+    else rc = pl.ll ? launch<PTC_ELS, 64, true>(backward, a, pl, st) : launch<PTC_ELS, 64, false>(backward, a, pl, st);
     if (rc == B2_OK) *tag_next += (unsigned)s.T + 1u;
     return rc;
 }

@@ -686,7 +686,9 @@ int b2_net_create(const char *network_json, int P, int maxT, unsigned seed, b2_n
 }
 void b2_net_destroy(b2_net *n) { delete n; }
 void b2_config_set_lstm_forget_gate_bias(float value) { b2::g_lstm_forget_gate_bias = value; }
-void b2_config_set_ptc_plan(int backward, int ll_chunks, int nc32_chunks) { b2::lstm_ptc_set_plan(backward != 0, ll_chunks, nc32_chunks); }
+void b2_config_set_ptc_plan(int backward, int ll_chunks, int nc32_chunks, int nc32_counter_chunks) {
+    b2::lstm_ptc_set_plan(backward != 0, ll_chunks, nc32_chunks, nc32_counter_chunks);
+}
 int b2_selftest_inject_status(b2_net *n, int code) {
     if (!n) return B2_ERR_BAD_ARG;
     B2_CUDA(cudaStreamSynchronize(n->net.stream));

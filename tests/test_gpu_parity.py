@@ -207,7 +207,7 @@ def test_persistent_tensor_core_recurrence(ls, bi, P, lens, mode):
 
 
 @pytest.mark.parametrize("P,lens", [(40, [9] * 20 + [8] * 10 + [5] * 10), (64, [7] * 40 + [6] * 20 + [2] * 4),
-                                    (100, [6] * 70 + [4] * 30), (130, [5] * 128 + [3, 2])])
+                                    (100, [6] * 70 + [4] * 30), (130, [5] * 128 + [3, 2]), (180, [4] * 170 + [3] * 10)])
 def test_chunk_plans_of_the_tensor_core_recurrence_agree(P, lens):
     """b2_config_set_ptc_plan changes how the sequences of a fraction are grouped into chunks and which exchange
     carries h and the partial errors between the blocks (step counters + bulk copies, or self-validating words collected
@@ -222,19 +222,19 @@ def test_chunk_plans_of_the_tensor_core_recurrence_agree(P, lens):
     want = run_kind(checker(), layers, P, lens, x, tg, w)
     runs = {}
     try:
-        for plan in [None, (1, 1), (2, 1), (2, 2), (1, 4), (3, 3)]:
+        for plan in [None, (1, 1), (2, 1), (2, 2), (1, 4), (3, 3), (1, 1, 8)]:
             if plan is None:
-                lib().b2_config_set_ptc_plan(0, 1, 1)
-                lib().b2_config_set_ptc_plan(1, 2, 5)
+                lib().b2_config_set_ptc_plan(0, 1, 1, 0)
+                lib().b2_config_set_ptc_plan(1, 2, 5, 6)
             else:
                 for backward in (0, 1):
-                    lib().b2_config_set_ptc_plan(backward, plan[0], plan[1])
+                    lib().b2_config_set_ptc_plan(backward, plan[0], plan[1], plan[2] if len(plan) > 2 else 0)
             paths = {}
             runs[plan] = run_gpu(layers, P, lens, x, tg, w, dict(recurrence=5, ffma=0), paths=paths)
             assert paths[1] == ("persistent_tensor_core", "persistent_tensor_core"), paths
     finally:
-        lib().b2_config_set_ptc_plan(0, 1, 1)
-        lib().b2_config_set_ptc_plan(1, 2, 5)
+        lib().b2_config_set_ptc_plan(0, 1, 1, 0)
+        lib().b2_config_set_ptc_plan(1, 2, 5, 6)
     parity.compare_run(layers, runs[None], want, "default plan, P%d" % P, lstm_pad_zero_lens=lens)
     for plan, got in runs.items():
         for key in got:
