@@ -212,8 +212,9 @@ int b2_net_update_weights(b2_net *net, float learning_rate, float momentum);
 /* The optimizer option of the reference (--optimizer; MacroDefine.hpp:32-37; gradient shaping in
  * SteepestDescentOptimizer::_updateWeights, SteepestDescentOptimizer.cu:127-194,306-395) applied by
  * every later update: 0 plain steepest descent (default), 1 AdaGrad, 2 gradient averaged over the
- * fraction's frames, 3 steepest descent that accumulates the AdaGrad statistics, 5 Adam
- * (beta1 0.9, beta2 0.999, epsilon 1e-8).  Setting it (re)initialises the statistics as the
+ * fraction's frames, 3 steepest descent that accumulates the AdaGrad statistics, 4 steepest descent
+ * whose learning rate the training run decays (the update itself is the plain one), 5 Adam
+ * (beta1 0.9, beta2 0.999, epsilon 1e-8).  What options 3 and 4 do when validation stalls: b2_optimizer_train.  Setting it (re)initialises the statistics as the
  * reference's Optimizer constructor does (Optimizer.cu:421-457).  With a data-parallel communicator
  * attached the frame count is summed over the ranks. */
 int b2_net_set_optimizer(b2_net *net, int option);
@@ -398,12 +399,16 @@ typedef struct {
     int validate_every;        /* --validate_every */
     int test_every;            /* --test_every */
     int batch_learning;        /* non-zero: the reference WITHOUT --hybrid_online_batch (one update per epoch) */
+    float second_learning_rate;/* --OptimizerSecondLR (reference default 0.01): the rate after option 3 has switched to AdaGrad */
+    float lr_decay_rate;       /* --LRDecayRate (reference default 0.1): factor applied by option 4 when validation stalls */
 } b2_optimizer_options;
 typedef struct {
     int finished, cur_epoch, epochs_since_lowest_error;
     float lowest_validation_error;
     float cur_training_error, cur_validation_error, cur_test_error;   /* sum over fractions of error / totalSequences */
     float cur_training_error_per_frame, cur_validation_error_per_frame, cur_test_error_per_frame;
+    float learning_rate;       /* the rate in use (changed by options 3 and 4 when validation stalls) */
+    int optimizer_option;      /* the net's option in use (3 turns into 1 when validation stalls) */
 } b2_optimizer_state;
 /* optimizers::SteepestDescentOptimizer(network, trainingSet, validationSet, testSet, maxEpochs,
  * maxEpochsNoBest, validateEvery, testEvery, learningRate, momentum) (Optimizer.cu:375-421);
@@ -413,7 +418,11 @@ int b2_optimizer_create(b2_optimizer **out, b2_net *net, b2_data *training_set, 
 void b2_optimizer_destroy(b2_optimizer *opt);
 /* Optimizer::train (Optimizer.cu:565-689): one epoch over the training set with weight updates,
  * then validation / test passes when due; stores the weights on a new lowest validation error,
- * restores the best weights and sets *finished when max_epochs or max_epochs_no_best is reached. */
+ * restores the best weights and sets *finished when max_epochs or max_epochs_no_best is reached.
+ * With the net's optimizer option 3 or 4 (b2_net_set_optimizer) a stall of max_epochs_no_best epochs does not end the run
+ * (Optimizer.cu:653-668): option 3 switches to AdaGrad (option 1, keeping the statistics gathered so far) with
+ * second_learning_rate and forgets the lowest validation error; option 4 multiplies the rate by lr_decay_rate; both
+ * restore the best weights and go on with epochs_since_lowest_error = 1. */
 int b2_optimizer_train(b2_optimizer *opt, int *finished);
 int b2_optimizer_get_state(const b2_optimizer *opt, b2_optimizer_state *state);
 /* Optimizer::saveState (Optimizer.cu:851-933, the "epochNNN.autosave" files): configuration and

@@ -398,7 +398,8 @@ class Net:
         return {names[i].decode(): (float(ms[i]), int(ln[i])) for i in range(n)}
 
     def set_optimizer(self, option):
-        """0 plain, 1 AdaGrad, 2 average gradient, 3 SGD accumulating AdaGrad statistics, 5 Adam"""
+        """0 plain, 1 AdaGrad, 2 average gradient, 3 SGD accumulating AdaGrad statistics (AdaGrad after a validation
+        stall), 4 SGD with learning-rate decay after a validation stall, 5 Adam"""
         _check(lib().b2_net_set_optimizer(self.h, option))
 
     def optimizer_stats(self, i):
@@ -582,7 +583,7 @@ def write_nc(path, seq_tags, seq_lengths, inputs, targets, output_means=None, ou
 class _OptimizerOptions(C.Structure):
     _fields_ = [("learning_rate", C.c_float), ("momentum", C.c_float), ("max_epochs", C.c_int),
                 ("max_epochs_no_best", C.c_int), ("validate_every", C.c_int), ("test_every", C.c_int),
-                ("batch_learning", C.c_int)]
+                ("batch_learning", C.c_int), ("second_learning_rate", C.c_float), ("lr_decay_rate", C.c_float)]
 
 
 class _OptimizerState(C.Structure):
@@ -590,7 +591,7 @@ class _OptimizerState(C.Structure):
                 ("lowest_validation_error", C.c_float), ("cur_training_error", C.c_float),
                 ("cur_validation_error", C.c_float), ("cur_test_error", C.c_float),
                 ("cur_training_error_per_frame", C.c_float), ("cur_validation_error_per_frame", C.c_float),
-                ("cur_test_error_per_frame", C.c_float)]
+                ("cur_test_error_per_frame", C.c_float), ("learning_rate", C.c_float), ("optimizer_option", C.c_int)]
 
 
 class Optimizer:
@@ -598,9 +599,10 @@ class Optimizer:
     train() runs one epoch (plus validation / test passes when due) and returns True when finished."""
 
     def __init__(self, net, training_set, validation_set=None, test_set=None, learning_rate=1e-5, momentum=0.9,
-                 max_epochs=-1, max_epochs_no_best=20, validate_every=1, test_every=1, batch_learning=False):
+                 max_epochs=-1, max_epochs_no_best=20, validate_every=1, test_every=1, batch_learning=False,
+                 second_learning_rate=0.01, lr_decay_rate=0.1):
         opt = _OptimizerOptions(learning_rate, momentum, max_epochs, max_epochs_no_best, validate_every, test_every,
-                                int(batch_learning))
+                                int(batch_learning), second_learning_rate, lr_decay_rate)
         self.h = C.c_void_p()
         self._keep = (net, training_set, validation_set, test_set)
         _check(lib().b2_optimizer_create(C.byref(self.h), net.h, training_set.h,

@@ -542,8 +542,9 @@ int NeuralNetwork::trainStepEmpty(float lr, float mom) {
 // Optimizer constructor, option part (optimizers/Optimizer.cu:421-457): AdaGrad statistics start at
 // OP_ADAGRADFACTOR, Adam's first and second moments at zero
 int NeuralNetwork::setOptimizerOption(int option) {
-    if (option != 0 && option != 1 && option != 2 && option != 3 && option != 5) {
-        set_error("b2_net_set_optimizer: option %d (0 plain, 1 AdaGrad, 2 average gradient, 3 SGD+AdaGrad statistics, 5 Adam)", option);
+    if (option < 0 || option > 5) {
+        set_error("b2_net_set_optimizer: option %d (0 plain, 1 AdaGrad, 2 average gradient, 3 SGD + AdaGrad statistics, 4 SGD with "
+                  "learning-rate decay, 5 Adam)", option);
         return B2_ERR_BAD_ARG;
     }
     optOption = option;
@@ -561,7 +562,9 @@ int NeuralNetwork::setOptimizerOption(int option) {
 
 int NeuralNetwork::updateWeights(float lr, float mom) {
     ProfScope ps(*this, "sgd_update");
-    if (optOption > 0) {
+    // option 4 (OPTIMIZATION_SGD_DECAY) updates like plain SGD; its schedule lives in the training run (b2_optimizer_train)
+    const bool adjust = optOption > 0 && optOption != 4;
+    if (adjust) {
         // frames of the fraction (summed over the ranks of a data-parallel job): the gradient is averaged over them
         B2_TRY(fill_value(fracLenDev, 1, (float)frac.realFrames, stream));
         if (dp) B2_TRY(dp_allreduce_sum(*this, fracLenDev, 1, stream));
@@ -574,7 +577,7 @@ int NeuralNetwork::updateWeights(float lr, float mom) {
         TrainableLayer *t = dynamic_cast<TrainableLayer *>(layers[i].get());
         if (!t) continue;
         float rate = t->learningRate() >= 0.0f ? t->learningRate() : lr;  // SteepestDescentOptimizer.cu:425-426
-        if (optOption > 0)
+        if (adjust)
             B2_TRY(sgd_update_opt(t->weights(), t->weightUpdates(), t->weightDeltas(), t->weightStats(), t->numWeights(), rate, mom,
                                   optOption, fracLenDev, adamBeta1Accum, adamBeta2Accum, stream));
         else

@@ -151,6 +151,7 @@ struct b2_optimizer {
     b2_optimizer_options opt{};
     // Optimizer<TDevice> members of the same names
     bool finished = false;
+    float learningRate = 0.0f;   // SteepestDescentOptimizer::m_learningRate (changeLR / adjustLR)
     int curEpoch = 0, epochsSinceLowestError = 0;
     float lowestValidationError = std::numeric_limits<float>::max();
     float curTrainingError = std::numeric_limits<float>::max();
@@ -272,6 +273,7 @@ int b2_optimizer_create(b2_optimizer **out, b2_net *net, b2_data *training_set, 
     o->validationSet = validation_set;
     o->testSet = test_set;
     o->opt = *options;
+    o->learningRate = options->learning_rate;
     if (o->opt.validate_every < 1) o->opt.validate_every = 1;
     if (o->opt.test_every < 1) o->opt.test_every = 1;
     o->bestWeights.resize(b2_net_impl(net)->layers.size());
@@ -292,8 +294,8 @@ int b2_optimizer_train(b2_optimizer *o, int *finished) {
         long long frames = 0;
         int nSeq = 0;
         long long nSteps = 0;
-        if (o->opt.batch_learning) B2_TRY(b2_net_train_epoch_batch(o->net, o->trainingSet, o->opt.learning_rate, o->opt.momentum, &err, &frames));
-        else B2_TRY(b2_net_train_epoch(o->net, o->trainingSet, o->opt.learning_rate, o->opt.momentum, &err, &frames));
+        if (o->opt.batch_learning) B2_TRY(b2_net_train_epoch_batch(o->net, o->trainingSet, o->learningRate, o->opt.momentum, &err, &frames));
+        else B2_TRY(b2_net_train_epoch(o->net, o->trainingSet, o->learningRate, o->opt.momentum, &err, &frames));
         o->curTrainingError = (float)err;
         B2_TRY(b2_data_info(o->trainingSet, &nSeq, &nSteps, nullptr, nullptr, nullptr, nullptr));
         o->curTrainingErrorPerFrame = o->curTrainingError * ((float)nSeq / (float)nSteps);
@@ -324,8 +326,24 @@ int b2_optimizer_train(b2_optimizer *o, int *finished) {
             B2_TRY(o->restoreWeights());
             o->finished = true;
         } else if (o->epochsSinceLowestError >= o->opt.max_epochs_no_best) {
-            B2_TRY(o->restoreWeights());
-            o->finished = true;
+            NeuralNetwork &nn = *b2_net_impl(o->net);
+            if (nn.optOption == 3) {
+                // OPTIMIZATION_STOCHASTIC_ADAGRAD: no best for N epochs, switch to AdaGrad on the statistics gathered so far;
+                // the count starts from 1 so that the restored weights are not stored again (Optimizer.cu:654-662)
+                nn.optOption = 1;
+                o->epochsSinceLowestError = 1;
+                o->lowestValidationError = std::numeric_limits<float>::max();
+                o->learningRate = o->opt.second_learning_rate;
+                B2_TRY(o->restoreWeights());
+            } else if (nn.optOption == 4) {
+                // OPTIMIZATION_SGD_DECAY (Optimizer.cu:663-668, SteepestDescentOptimizer::adjustLR)
+                o->epochsSinceLowestError = 1;
+                o->learningRate *= o->opt.lr_decay_rate;
+                B2_TRY(o->restoreWeights());
+            } else {
+                B2_TRY(o->restoreWeights());
+                o->finished = true;
+            }
         }
     }
     if (finished) *finished = o->finished ? 1 : 0;
@@ -344,6 +362,8 @@ int b2_optimizer_get_state(const b2_optimizer *o, b2_optimizer_state *s) {
     s->cur_training_error_per_frame = o->curTrainingErrorPerFrame;
     s->cur_validation_error_per_frame = o->curValidationErrorPerFrame;
     s->cur_test_error_per_frame = o->curTestErrorPerFrame;
+    s->learning_rate = o->learningRate;
+    s->optimizer_option = b2_net_impl(o->net)->optOption;
     return B2_OK;
 }
 

@@ -185,6 +185,51 @@ def test_optimizer_options_follow_the_reference_formulas(option):
     net.close()
 
 
+@pytest.mark.parametrize("option", [3, 4])
+def test_a_validation_stall_changes_the_schedule_of_options_3_and_4_instead_of_ending_the_run(tmp_path, option):
+    """Optimizer::train, branch `m_epochsSinceLowestError >= m_maxEpochsNoBest` (Optimizer.cu:653-668).  Option 3
+    (SGD while gathering AdaGrad statistics) turns into AdaGrad with the second learning rate and forgets the lowest
+    validation error; option 4 multiplies the learning rate by the decay rate; both restore the best weights, go on
+    with epochs_since_lowest_error = 1 and do not finish.  A learning rate too small to change an fp32 weight makes
+    the validation error stall exactly."""
+    import b2lstm
+    from b2lstm import workloads
+    w_true = np.random.default_rng(0).standard_normal((7, 3)).astype(np.float32)
+    train = corpus(tmp_path, "train.nc", [20, 35, 28, 31, 25, 22, 38, 27], 1, w_true)
+    valid = corpus(tmp_path, "valid.nc", [30, 24, 33], 2, w_true)
+    P = 4
+    w = workloads.make_weights(LAYERS, 9, 0.1)
+    net = b2lstm.Net(LAYERS, P, 40)
+    for i, wi in w.items():
+        net.set_weights(i, wi)
+    net.set_optimizer(option)
+    tr, va = b2lstm.DataSet(train, P), b2lstm.DataSet(valid, P)
+    opt = b2lstm.Optimizer(net, tr, va, learning_rate=1e-20, momentum=0.0, max_epochs=8, max_epochs_no_best=2,
+                           second_learning_rate=0.02, lr_decay_rate=0.25)
+    states = []
+    for _ in range(3):
+        assert not opt.train()
+        states.append(opt.state)
+    assert [s["epochs_since_lowest_error"] for s in states] == [0, 1, 1]      # third epoch: 2 >= 2, the branch sets 1
+    assert states[0]["cur_validation_error"] == states[1]["cur_validation_error"] == states[2]["cur_validation_error"]
+    assert states[1]["optimizer_option"] == option and states[1]["learning_rate"] == np.float32(1e-20)
+    for i, wi in w.items():
+        assert np.array_equal(net.get_weights(i), wi)                          # best weights restored (they never moved)
+    if option == 3:
+        assert states[2]["optimizer_option"] == 1 and states[2]["learning_rate"] == np.float32(0.02)
+        assert states[2]["lowest_validation_error"] == np.finfo(np.float32).max
+        assert not opt.train()                                                  # AdaGrad epoch on the gathered statistics
+        s = opt.state
+        assert s["lowest_validation_error"] == s["cur_validation_error"] and s["epochs_since_lowest_error"] == 0
+        assert any(not np.array_equal(net.get_weights(i), wi) for i, wi in w.items())
+    else:
+        assert states[2]["optimizer_option"] == 4
+        assert states[2]["learning_rate"] == np.float32(np.float32(1e-20) * np.float32(0.25))
+        assert states[2]["lowest_validation_error"] == states[0]["cur_validation_error"]
+    opt.close()
+    net.close()
+
+
 def test_batch_learning_sums_the_epoch_and_updates_once(tmp_path):
     """The reference without --hybrid_online_batch: the gradients of all fractions of an epoch are summed
     and ONE update follows.  Checked against the sum of the per-fraction gradients taken separately."""
