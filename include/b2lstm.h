@@ -385,6 +385,12 @@ int b2_net_export_json(b2_net *net, char *buf, size_t capacity, size_t *needed, 
 /* NeuralNetwork::saveNetwork (NeuralNetwork.cpp:4104-4125): the same document into a file
  * (trained_network.jsn). */
 int b2_net_save_network(b2_net *net, const char *filename, int digits);
+/* NeuralNetwork::printWeightMatrix (NeuralNetwork.cpp:3792-3880; read back by pyTools/ioTools/nnio.py
+ * ReadCURRENNTWeight): the weights as one file of native floats.  Header: the number of layers with weights, then
+ * per layer {number of weights, size, preceding layer's size, input weights per block, internal weights per block}
+ * (and, when with_type_codes is non-zero, the reference's type code 0 feedforward_tanh, 1 _logistic, 2 _identity,
+ * 3 _relu, 4 lstm, 5 blstm); then every layer's weight vector in layer order. */
+int b2_net_save_weights_binary(b2_net *net, const char *filename, int with_type_codes);
 /* The momentum term of SteepestDescentOptimizer (m_weightDeltas, SteepestDescentOptimizer.cu:421-438)
  * of one layer, host <-> device; part of the autosave state. */
 int b2_net_get_weight_deltas(b2_net *net, int layer, float *host_out);

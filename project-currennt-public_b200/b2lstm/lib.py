@@ -47,6 +47,7 @@ SIGNATURES = {
     "b2_lstm_synchronize": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b2_net_create": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_uint, C.POINTER(C.c_void_p)]),
     "b2_config_set_lstm_forget_gate_bias": (None, [C.c_float]),
+    "b2_net_save_weights_binary": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
     "b2_config_set_ptc_plan": (None, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "b2_net_destroy": (None, [C.c_void_p]),
     "b2_net_parallel_sequences": (C.c_int, [C.c_void_p]),
@@ -417,6 +418,10 @@ class Net:
         buf = C.create_string_buffer(need.value)
         _check(lib().b2_net_export_json(self.h, buf, need.value, None, digits))
         return buf.value.decode()
+
+    def save_weights_binary(self, filename, with_type_codes=False):
+        """NeuralNetwork::printWeightMatrix: header + raw float weights (pyTools/ioTools/nnio.py reads it)"""
+        _check(lib().b2_net_save_weights_binary(self.h, os.fsencode(filename), int(with_type_codes)))
 
     def save_network(self, filename, digits=0):
         _check(lib().b2_net_save_network(self.h, os.fsencode(filename), digits))

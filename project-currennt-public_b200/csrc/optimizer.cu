@@ -246,6 +246,53 @@ int b2_net_save_network(b2_net *net, const char *filename, int digits) {
     return write_file(filename, out);
 }
 
+// NeuralNetwork::printWeightMatrix (NeuralNetwork.cpp:3792-3880): all numbers as native floats.  Header: the number of
+// layers with weights, then per layer {weights, size, preceding size, input weights per block, internal weights per
+// block [, type code when with_type_codes]}; then every layer's weight vector in layer order.
+int b2_net_save_weights_binary(b2_net *net, const char *filename, int with_type_codes) {
+    if (!net || !filename) { set_error("b2_net_save_weights_binary: null pointer"); return B2_ERR_BAD_ARG; }
+    NeuralNetwork &nn = *b2_net_impl(net);
+    std::vector<float> head, body, w;
+    int n = 0;
+    for (size_t i = 0; i < nn.layers.size(); ++i) {
+        Layer *l = nn.layers[i].get();
+        TrainableLayer *t = dynamic_cast<TrainableLayer *>(l);
+        if (!t) continue;
+        const std::string &ty = l->type();
+        const bool lstm = ty == "lstm" || ty == "blstm";
+        // the TrainableLayer constructor arguments of the layer classes (FeedForwardLayer.cu: 1, 0; LstmLayer.cu: 4, (bidirectional ? 2 : 4) * size + 3)
+        const int inPerBlock = lstm ? 4 : 1;
+        const int internalPerBlock = lstm ? (ty == "blstm" ? 2 : 4) * l->size() + 3 : 0;
+        ++n;
+        head.push_back((float)t->numWeights());
+        head.push_back((float)l->size());
+        head.push_back((float)l->precedingLayer()->size());
+        head.push_back((float)inPerBlock);
+        head.push_back((float)internalPerBlock);
+        if (with_type_codes) {
+            const char *names[6] = {"feedforward_tanh", "feedforward_logistic", "feedforward_identity", "feedforward_relu", "lstm", "blstm"};
+            int code = -1;
+            for (int c = 0; c < 6; ++c)
+                if (ty == names[c]) code = c;
+            if (code < 0) { set_error("b2_net_save_weights_binary: no type code for layer type '%s'", ty.c_str()); return B2_ERR_BAD_ARG; }
+            head.push_back((float)code);
+        }
+        if (t->numWeights()) {
+            B2_TRY(fetch_weights(nn, t, w));
+            body.insert(body.end(), w.begin(), w.end());
+        }
+    }
+    FILE *f = fopen(filename, "wb");
+    if (!f) { set_error("Cannot open file '%s'", filename); return B2_ERR_BAD_ARG; }
+    const float count = (float)n;
+    size_t done = fwrite(&count, sizeof(float), 1, f);
+    done += fwrite(head.data(), sizeof(float), head.size(), f);
+    done += fwrite(body.data(), sizeof(float), body.size(), f);
+    const int rc = fclose(f);
+    if (done != 1 + head.size() + body.size() || rc != 0) { set_error("Cannot write file '%s'", filename); return B2_ERR_BAD_ARG; }
+    return B2_OK;
+}
+
 int b2_net_get_weight_deltas(b2_net *net, int layer, float *host) {
     NeuralNetwork &nn = *b2_net_impl(net);
     TrainableLayer *t = (net && layer >= 0 && layer < (int)nn.layers.size()) ? dynamic_cast<TrainableLayer *>(nn.layers[layer].get()) : nullptr;

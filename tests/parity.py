@@ -102,3 +102,25 @@ def compare_run(layers, got, want, what, lstm_pad_zero_lens=None, P=None, loss_r
                 # padding frames at or beyond the shortest sequence's length are forced to exact zero
                 t0 = max(Lp, min(lstm_pad_zero_lens))
                 assert not o[t0:, p].any(), "%s layer %d: non-zero output on padding of sequence %d" % (what, i, p)
+
+
+def weight_dump_bytes(layers, weights, with_type_codes=False):
+    """The file NeuralNetwork::printWeightMatrix writes (NeuralNetwork.cpp:3792-3880 of the reference), restated: native
+    floats; the number of layers with weights, per layer {weights, size, preceding size, input weights per block, internal
+    weights per block [, type code]}, then the weight vectors.  `weights`: {layer index: flat float32 array}."""
+    codes = {"feedforward_tanh": 0, "feedforward_logistic": 1, "feedforward_identity": 2, "feedforward_relu": 3, "lstm": 4, "blstm": 5}
+    head, body = [], []
+    for i, l in enumerate(layers):
+        if i not in weights:
+            continue
+        lstm = l["type"] in ("lstm", "blstm")
+        in_per_block = 4 if lstm else 1
+        internal = ((2 if l["type"] == "blstm" else 4) * l["size"] + 3) if lstm else 0
+        w = np.asarray(weights[i], np.float32)
+        assert w.size == l["size"] * (in_per_block * (layers[i - 1]["size"] + 1) + internal)
+        head += [w.size, l["size"], layers[i - 1]["size"], in_per_block, internal]
+        if with_type_codes:
+            head.append(codes[l["type"]])
+        body.append(w)
+    n = len(body)
+    return np.concatenate([np.array([n] + head, np.float32)] + body).tobytes()

@@ -58,6 +58,23 @@ def test_export_json_round_trips_exactly_and_keeps_the_reference_layout():
     net2.close()
 
 
+def test_binary_weight_dump_has_the_layout_of_the_reference(tmp_path):
+    """b2_net_save_weights_binary = NeuralNetwork::printWeightMatrix; the expected bytes come from the restatement that
+    tests/test_weights_binary.py pins to the reference's own reader."""
+    import b2lstm
+    import parity
+    from b2lstm import workloads
+    w = workloads.make_weights(LAYERS, 5, 0.3)
+    net = b2lstm.Net(LAYERS, 2, 8)
+    for i, wi in w.items():
+        net.set_weights(i, wi)
+    for codes in (False, True):
+        path = str(tmp_path / ("w%d.bin" % codes))
+        net.save_weights_binary(path, with_type_codes=codes)
+        assert open(path, "rb").read() == parity.weight_dump_bytes(LAYERS, w, with_type_codes=codes)
+    net.close()
+
+
 def test_training_run_stops_on_validation_error_and_restores_best_weights(tmp_path):
     import b2lstm
     from b2lstm import workloads
