@@ -159,6 +159,12 @@ int b2_net_create(const char *network_json, int parallel_sequences, int max_seq_
  * every forget-gate bias of the (b)lstm layers that b2_net_create initialises at random from now on (layers whose
  * weights come from the JSON are left alone).  Process-wide, like the reference's Configuration; default 0. */
 void b2_config_set_lstm_forget_gate_bias(float value);
+/* --weights_uniform_min / --weights_uniform_max (Configuration.cpp:666-670; defaults -0.1, 0.1): the range of the random
+ * weights of layers without a "weights" section.  b2_net_create draws them as the reference does with its default
+ * weights_dist = uniform (layers/TrainableLayer.cu:219-233): one mt19937 seeded with `seed` for all layers in order, each
+ * weight = boost::random::uniform_real_distribution<float>(0, max - min)(gen) + min (restated from Boost.Random).
+ * Process-wide; call before b2_net_create. */
+void b2_config_set_weights_uniform(float min, float max);
 
 /* Tuning of the persistent tensor-core recurrence (no counterpart in the reference).  The sequences of a fraction are
  * processed in chunks of 32 or 64; the chunks of a group of blocks are in flight together.

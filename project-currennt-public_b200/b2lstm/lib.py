@@ -47,6 +47,7 @@ SIGNATURES = {
     "b2_lstm_synchronize": (C.c_int, [C.c_void_p, C.c_void_p]),
     "b2_net_create": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_uint, C.POINTER(C.c_void_p)]),
     "b2_config_set_lstm_forget_gate_bias": (None, [C.c_float]),
+    "b2_config_set_weights_uniform": (None, [C.c_float, C.c_float]),
     "b2_net_save_weights_binary": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
     "b2_config_set_ptc_plan": (None, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "b2_net_destroy": (None, [C.c_void_p]),

@@ -18,6 +18,7 @@ namespace b2 {
 static thread_local char g_err[1024] = "";
 unsigned long long g_launches = 0;
 float g_lstm_forget_gate_bias = 0.0f;   // the process-wide option, like the reference's Configuration singleton
+float g_weights_uniform_min = -0.1f, g_weights_uniform_max = 0.1f;   // --weights_uniform_min / --weights_uniform_max (Configuration.cpp:666-670)
 
 void set_error(const char *fmt, ...) {
     va_list ap;
@@ -352,9 +353,21 @@ int NeuralNetwork::create(const char *networkJson, int P_, int maxT_, unsigned s
     gradReady.resize(layers.size());
     for (size_t i = 0; i < layers.size(); ++i) B2_CUDA(cudaEventCreateWithFlags(&gradReady[i], cudaEventDisableTiming));
 
-    // weights: from the "weights" section where present (TrainableLayer.cu:135-205), else uniform random
+    // weights: from the "weights" section where present (TrainableLayer.cu:135-205), else uniform random as the reference
+    // draws them (TrainableLayer.cu:219-233): ONE mt19937 seeded with the random seed serves all layers in order, and each
+    // weight is boost::random::uniform_real_distribution<float>(0, max - min)(gen) + min.  That distribution, restated from
+    // Boost.Random (absent here, so the stream is not pinned against Boost itself): float(draw) / (float(2^32 - 1) + 1) *
+    // range, drawn again while the rounded result reaches the range.
     std::mt19937 gen(seed);
-    std::uniform_real_distribution<float> dist(-0.08f, 0.08f);
+    const float wmin = g_weights_uniform_min, wrange = g_weights_uniform_max - g_weights_uniform_min;
+    auto dist = [wmin, wrange](std::mt19937 &g) {
+        for (;;) {
+            const float numerator = static_cast<float>(g());
+            const float divisor = static_cast<float>(0xffffffffu) + 1.0f;
+            const float result = numerator / divisor * wrange + 0.0f;
+            if (result < wrange || !(wrange > 0.0f)) return result + wmin;
+        }
+    };
     const json::Value *wsec = doc.find("weights");
     for (size_t i = 0; i < layers.size(); ++i) {
         TrainableLayer *t = dynamic_cast<TrainableLayer *>(layers[i].get());
@@ -689,6 +702,7 @@ int b2_net_create(const char *network_json, int P, int maxT, unsigned seed, b2_n
 }
 void b2_net_destroy(b2_net *n) { delete n; }
 void b2_config_set_lstm_forget_gate_bias(float value) { b2::g_lstm_forget_gate_bias = value; }
+void b2_config_set_weights_uniform(float min, float max) { b2::g_weights_uniform_min = min; b2::g_weights_uniform_max = max; }
 void b2_config_set_ptc_plan(int backward, int ll_chunks, int nc32_chunks, int nc32_counter_chunks) {
     b2::lstm_ptc_set_plan(backward != 0, ll_chunks, nc32_chunks, nc32_counter_chunks);
 }

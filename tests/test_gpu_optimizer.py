@@ -279,6 +279,36 @@ def test_batch_learning_sums_the_epoch_and_updates_once(tmp_path):
     net.close()
 
 
+def test_random_weights_follow_the_reference_stream():
+    """Layers without a weights section are initialised as layers/TrainableLayer.cu:219-233 does with the default
+    uniform distribution: one mt19937 (seed = --random_seed) for all layers in order, each weight
+    boost::random::uniform_real_distribution<float>(0, max - min)(gen) + min.  Checked against a numpy restatement on
+    the generator's raw 32-bit outputs (numpy's legacy RandomState seeds the same init_genrand; its first output for seed
+    5489, 3499211612, is the generator's published known answer)."""
+    import b2lstm
+    from b2lstm.lib import lib
+    assert int(np.random.RandomState(5489)._bit_generator.random_raw(1)[0]) == 3499211612
+    for seed, (lo, hi) in [(0, (-0.1, 0.1)), (77, (-0.05, 0.3))]:
+        lib().b2_config_set_weights_uniform(lo, hi)
+        try:
+            net = b2lstm.Net(LAYERS, 2, 8, seed=seed)
+        finally:
+            lib().b2_config_set_weights_uniform(-0.1, 0.1)
+        raw = np.random.RandomState(seed)._bit_generator.random_raw(20000).astype(np.uint32)
+        rng_f = np.float32(np.float32(hi) - np.float32(lo))
+        cand = (raw.astype(np.float32) / np.float32(4294967296.0)) * rng_f          # float arithmetic throughout
+        cand = cand[cand < rng_f]                                                    # a draw that rounds up to the range is repeated
+        want = cand + np.float32(lo)
+        k = 0
+        for i, l in enumerate(LAYERS):
+            if l["type"] in ("input", "sse"):
+                continue
+            got = net.get_weights(i)
+            assert np.array_equal(got, want[k:k + got.size]), (seed, i)
+            k += got.size
+        net.close()
+
+
 def test_forget_gate_bias_option_shifts_only_the_forget_biases_of_fresh_lstm_layers():
     """--lstm_forget_gate_bias of the reference (layers/LstmLayer.cu:1147-1161): the value is added to the forget-gate
     biases of randomly initialised (b)lstm layers and to nothing else; layers read from a weights section keep theirs."""
