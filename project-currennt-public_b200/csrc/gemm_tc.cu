@@ -48,7 +48,7 @@ constexpr int TC_MAX_BATCH = 8;
 template <bool F16>
 struct Mode {
     static constexpr int BK = F16 ? 64 : 32;            // contraction positions per slab: one 128-byte swizzle row
-    static constexpr int SEG = F16 ? 2 : 4;             // slabs per drained accumulator segment (128 positions)
+    static constexpr int SEG = 4;                       // slabs per drained accumulator segment: 16 main MMAs (256 resp. 128 positions)
     static constexpr int MNBOX = F16 ? 64 : 32;         // MN-major operands arrive as column blocks one swizzle row wide
     static constexpr int MNBOX_BYTES = BK * 128;        // ... of BK rows each
 };
