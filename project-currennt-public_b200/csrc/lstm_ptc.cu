@@ -12,8 +12,8 @@
 // [-1, 1]: h = tanh(c) * og, and the deltas are clipped by helpers::limitedError), and per direction
 // 2^13 <= max|w| * S < 2^14 for the recurrent weights.  Three kind::f16 MMAs per product, a_hi*b_hi into a main
 // accumulator and a_lo*b_hi + a_hi*b_lo into a cross-term accumulator, both fp32 in tensor memory; the result
-// (main + cross * 2^-11) / S carries 22 mantissa bits of each operand, like the 3xTF32 split of the large GEMMs,
-// at half the shared memory and half the instructions.  An accumulator never takes more than 8 main-term MMAs
+// (main + cross * 2^-11) / S carries 22 mantissa bits of each operand, the same scheme as the large GEMMs
+// (gemm_tc.cu).  An accumulator never takes more than 8 main-term MMAs
 // (K = 128): tensor-memory accumulation truncates, so longer contractions are split over blocks and added by CUDA cores.
 //
 // Measured on B200: a tcgen05.mma costs its issuing thread about 85 cycles whatever M and N are (up to N = 128), so
@@ -31,13 +31,18 @@
 //             and fetches the whole operand with ONE bulk copy (cp.async.bulk) that completes on the MMA's barrier.
 //   backward: the same weight tile, stored transposed, is operand A of  e[k] = sum_c W[c][k] delta[c]  with the
 //             block's own row tile as the contraction range: the four blocks of a row tile compute 8 units' gate
-//             deltas each and hand them to each other through distributed shared memory as fp16 operand chunks;
+//             deltas each, write them as fp16 hi / lo into their own operand buffer (stored WITHOUT swizzle, so that
+//             a block's share is contiguous per gate) and hand them to each other through distributed shared memory
+//             (bulk copies issued by a sender warp, or st.async from the cell warps where the latency is in the chain);
 //             block (r, q) turns them into partial output errors of source units [128q, 128q + 128), publishes them
 //             (fp32) with a release store of its step counter, and the block that owns a unit adds the 16 partials
 //             in a fixed order (bitwise deterministic) and runs the error functor.
 // Groups of sequences ("chunks" of N) are independent; a group of blocks works on several chunks in turn, so that
 // the exchange of one chunk overlaps the tensor-core work of another.  Warps are specialised (poll / MMA issue /
-// tensor-memory drain / cell math) and hand buffers to each other through mbarriers.
+// tensor-memory drain / cell math / publisher; backward also sender and reduce) and hand buffers to each other through
+// mbarriers.  With few chunks per group a step is a chain of latencies, and the exchange through L2 uses
+// self-validating words {step tag : payload} instead of counters and bulk copies (template parameter LL; make_plan
+// chooses per sweep, every choice gives the same bits).
 //
 // Every wait is bounded (cycle budget of about two seconds, poll-round limit for the step counters): on expiry the
 // thread records B2_ERR_STEP_TIMEOUT in the layer's status word and raises the block's give-up flag, every role
@@ -65,7 +70,7 @@ constexpr uint32_t A_HALF = 32768, A_BYTES = 65536;   // weight image: hi, lo of
 
 // Warp roles.  Forward: warp 0 MMA issue, 1 poll + operand fetch, 2-5 drain, then the cell-math warps, the publisher, and
 // a second MMA-issue warp.  Backward: warp 0 MMA issue, then the cell-math warps, 4 drain warps, 4 gather + reduce warps,
-// the publisher, and a second MMA-issue warp.  Two issuers: measured with a probe, 24 MMAs cost one issuing thread 1870
+// the publisher, a second MMA-issue warp and the sender.  Two issuers: measured with a probe, 24 MMAs cost one issuing thread 1870
 // cycles, two threads of different warps (12 each, accumulators of their own) 940.
 // With several chunks per group the cell math bounds the throughput, so that variant gets twice the cell warps; with
 // one chunk per group (LL) a step is a chain of latencies and fewer, fatter threads are as good.
